@@ -45,6 +45,8 @@ class EngineConfig:
     seed: int = 0
     log_stats: bool = True
     tokenizer_path: Optional[str] = None
+    dtype: Optional[str] = None               # override the checkpoint's compute dtype (bfloat16 | float32)
+    num_state_slots: Optional[int] = None     # recurrent-state slots (models with per-sequence state); None: auto
 
     @property
     def world_size(self) -> int:

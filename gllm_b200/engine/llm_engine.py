@@ -76,7 +76,7 @@ class LLM:
             model_max_length=model_max_length, mm_processor_min_pixels=mm_processor_min_pixels,
             mm_processor_max_pixels=mm_processor_max_pixels, **extra)
         cfg = self.cfg
-        self.loader = ModelLoader(cfg.model_path, cfg.load_format)
+        self.loader = ModelLoader(cfg.model_path, cfg.load_format, dtype=cfg.dtype)
         self.tokenizer = load_tokenizer(cfg.tokenizer_path or cfg.model_path)
         self.finish_tokens = self.loader.eos_token_ids()
         gen = self.loader.generation_config

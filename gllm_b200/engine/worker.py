@@ -76,8 +76,14 @@ class Worker(ProfilerMixin):
         self.runner = ModelRunner(cfg, self.loader)
         self.runner.init(device, progress=self._progress)
         if self.rank == 0:
-            mm_cls = PrefixMemoryManager if cfg.enable_prefix_caching else MemoryManager
-            self.mm = mm_cls(self.runner.num_pages, cfg.page_size, reserve_dummy_page=True)
+            slots = self.runner.num_state_slots
+            if slots:
+                # recurrent state cannot be rebuilt from cached pages: no prefix cache for such models
+                self.mm = MemoryManager(self.runner.num_pages, cfg.page_size, reserve_dummy_page=True,
+                                        num_state_slots=slots)
+            else:
+                mm_cls = PrefixMemoryManager if cfg.enable_prefix_caching else MemoryManager
+                self.mm = mm_cls(self.runner.num_pages, cfg.page_size, reserve_dummy_page=True)
             self.scheduler = Scheduler(self.mm, pp_size=cfg.pp_size, world_size=cfg.world_size,
                                        schedule_method=cfg.schedule_method, maxd=cfg.maxd, maxp=cfg.maxp,
                                        minp=cfg.minp, iterp=cfg.iterp, kvthresh=cfg.kvthresh,

@@ -1,0 +1,100 @@
+"""Trace replay: feed given token ids through the engine step by step and write the logits of chosen positions.
+
+    bin/trace_run --model DIR --dtype bfloat16|float32 --out DIR --max-tokens N
+
+Reads one JSON object per line from standard input,
+    {"step": 0, "entries": [{"id": "a", "tokens": [5, 17, 3], "want": [0, 2]}], "end": ["a"]}
+runs all entries of a step as ONE micro-batch (prompt portions beside single decode tokens) through the engine's
+worker — its scheduler bookkeeping, page and state-slot managers, batch builder, model runner and kernels — writes
+`<out>/<step>.f32` ([wanted rows, vocab] little-endian fp32, in entry / want order) when something is wanted, and
+prints `done <step>`. Nothing is sampled. Requests named in "end" give their pages and slots back after the step.
+The cache pool holds --max-tokens tokens (+ the padding page) and four recurrent-state slots, so both are re-used.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import numpy as np
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(prog="trace_run")
+    ap.add_argument("--model", required=True)
+    ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    ap.add_argument("--out", required=True)
+    ap.add_argument("--max-tokens", type=int, required=True)
+    ap.add_argument("--device", default=None)
+    ap.add_argument("--page-size", type=int, default=16)
+    ap.add_argument("--state-slots", type=int, default=4)
+    a = ap.parse_args(argv)
+
+    import torch
+    from gllm_b200.config import EngineConfig
+    from gllm_b200.engine.worker import Worker
+    from gllm_b200.input_data import build_batch
+    from gllm_b200.model_loader import ModelLoader
+    from gllm_b200.sequence import Sequence
+
+    torch.backends.cuda.matmul.allow_tf32 = False
+    torch.backends.cudnn.allow_tf32 = False
+    ps = a.page_size
+    pages = (a.max_tokens + ps - 1) // ps + 1            # + the padding page
+    cfg = EngineConfig(model_path=a.model, dtype=a.dtype, page_size=ps, maxp=max(a.max_tokens, 64), maxd=64,
+                       num_gpu_pages=pages, num_cpu_pages=pages, model_max_length=max(a.max_tokens, 64),
+                       enable_prefix_caching=False, disable_cuda_graph=True, async_schedule=False, kvthresh=0.0,
+                       log_stats=False, launch_mode="inproc", device=a.device, num_state_slots=a.state_slots)
+    loader = ModelLoader(cfg.model_path, cfg.load_format, dtype=cfg.dtype)
+    worker = Worker(cfg, 0, 0, comm=None, loader=loader).init()
+    sch, runner = worker.scheduler, worker.runner
+    vocab = runner.spec.vocab_size
+    os.makedirs(a.out, exist_ok=True)
+    live = {}
+    next_id = 0
+    for line in sys.stdin:
+        line = line.strip()
+        if not line:
+            continue
+        msg = json.loads(line)
+        plan, wants = [], {}
+        for e in msg.get("entries", []):
+            toks = [int(t) for t in e["tokens"]]
+            if not toks:
+                continue
+            seq = live.get(e["id"])
+            if seq is None:
+                seq = Sequence(next_id, toks, [], output_len=1 << 30, ignore_eos=True, top_k=1)
+                next_id += 1
+                live[e["id"]] = seq
+            else:
+                seq.token_ids.extend(toks)
+            plan.append((seq, len(toks)))
+            wants[seq.seq_id] = [int(w) for w in e.get("want", [])]
+        if plan:
+            entries = sch.schedule_explicit(plan)
+            batch = build_batch(entries, ps, vocab, batch_id=int(msg.get("step", 0)))
+            first_row = {ent.seq.seq_id: int(batch.query_start_loc[i]) for i, ent in enumerate(entries)}
+            rows = [first_row[seq.seq_id] + w for seq, _ in plan for w in wants[seq.seq_id]]
+            batch.logits_idx = np.asarray(rows, dtype=np.int32)
+            logits = runner.step_logits(batch)
+            if rows:
+                out = logits.detach().to("cpu", torch.float32).contiguous().numpy().astype("<f4")
+                tmp = os.path.join(a.out, "%s.f32.tmp" % msg["step"])
+                out.tofile(tmp)
+                os.replace(tmp, os.path.join(a.out, "%s.f32" % msg["step"]))
+            elif runner.device.type == "cuda":
+                torch.cuda.synchronize()
+            sch.complete_explicit([live.pop(i) for i in msg.get("end", []) if i in live])
+        else:
+            for i in msg.get("end", []):
+                if i in live:
+                    sch.mm.free(live.pop(i))
+        sys.stdout.write("done %s\n" % msg["step"])
+        sys.stdout.flush()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -58,6 +58,7 @@ class BatchArrays:
     # lookahead (async scheduling): row i takes its input token from element feed_src[i] of the PREVIOUS step's
     # device-side sampler output instead of `tokens[i]` (which holds a placeholder)
     feed_src: Optional[np.ndarray] = None
+    rec_slots: Optional[np.ndarray] = None   # int32 [B] recurrent-state slot of every sequence (models that keep one)
     emit_ids: Optional[list] = None  # driver-local: sequence id per EMITTING entry (order of the sampler output)
     seq_ids: Optional[list] = None  # driver-local: sequence id per row (incremental decode batches); not sent
     pt_gens: Optional[list] = None  # driver-local: Sequence.pt_gen per row when the block table rows were written
@@ -71,7 +72,7 @@ class BatchArrays:
         (16-byte aligned sections) so a batch costs two zmq frames per peer instead of one per array."""
         names = ["tokens", "positions", "slot_mapping", "block_table", "seq_lens", "query_start_loc",
                  "logits_idx", "emit_seq", "temperature", "top_k", "top_p", "rep_penalty", "state_slot"]
-        opt = ["seen_rows", "seen_tokens", "clear_slots", "feed_src"]
+        opt = ["seen_rows", "seen_tokens", "clear_slots", "feed_src", "rec_slots"]
         hdr = {"scalars": (self.num_decode_seqs, self.num_seqs, self.num_tokens, self.max_q_len,
                            self.max_seq_len, self.all_greedy, self.need_penalty, self.batch_id),
                "arrays": [], "mm": self.mm}
@@ -159,7 +160,7 @@ def _build_decode_fast(entries, page_size: int, batch_id: int, prev: "BatchArray
     slots = bt[rows, blk] * page_size + starts % page_size
     seq_lens = starts + 1
     feed = perm.astype(np.int32) if (tokens < 0).any() else None   # lookahead rows: token still on the device
-    return BatchArrays(feed_src=feed,
+    return BatchArrays(feed_src=feed, rec_slots=prev.rec_slots[perm] if prev.rec_slots is not None else None,
         tokens=tokens, positions=starts, slot_mapping=slots.astype(np.int32), block_table=bt, seq_lens=seq_lens,
         query_start_loc=prev.query_start_loc[:b + 1], logits_idx=prev.logits_idx[:b], emit_seq=prev.emit_seq[:b],
         temperature=prev.temperature[perm], top_k=prev.top_k[perm], top_p=prev.top_p[perm],
@@ -250,7 +251,9 @@ def build_batch(entries, page_size: int, vocab_size: int, batch_id: int = 0, mro
     if mrope:
         from gllm_b200.models.multimodal import batch_mm_payload
         mm = batch_mm_payload(entries, qsl)
+    rec = np.fromiter((e.seq.rec_slot for e in entries), dtype=np.int32, count=b)
     return BatchArrays(
+        rec_slots=rec if b and int(rec.max()) >= 0 else None,
         tokens=tokens, positions=positions, slot_mapping=slots, block_table=block_table, seq_lens=seq_lens,
         query_start_loc=qsl, logits_idx=np.asarray(logits_idx, dtype=np.int32),
         emit_seq=np.asarray(emit_seq, dtype=np.int32), temperature=np.asarray(temperature, dtype=np.float32),
@@ -294,7 +297,7 @@ class InputData:
         self._block_table = buf((max_seqs, max_blocks), i32)
         self._seq_lens = buf((max_seqs,), i32)
         self._qsl = buf((max_seqs + 1,), i32)
-        self._logits_idx = buf((max_seqs,), i32)
+        self._logits_idx = buf((max(max_seqs, max_tokens),), i32)   # any row may be asked for (logit tracing)
         self._temperature = buf((max_seqs,), f32)
         self._top_k = buf((max_seqs,), i32)
         self._top_p = buf((max_seqs,), f32)
@@ -302,6 +305,8 @@ class InputData:
         self._state_slot = buf((max_seqs,), i32)
         self._tok_seq = buf((max_tokens,), i32)
         self._feed = buf((max_seqs,), i32)
+        self._rec_slots = buf((max_seqs,), i32)
+        self.dummy_state_slot = 0   # set by the runner: the slot CUDA-graph padding rows scribble on
         self.need_tok_seq = False  # MLA attention wants token -> sequence for mixed / prefill batches
         self.batch: Optional[BatchArrays] = None
         self.num_tokens = self.num_seqs = self.num_decode_seqs = self.num_emit = 0
@@ -346,6 +351,8 @@ class InputData:
             self._put(self._tok_seq, np.repeat(np.arange(batch.num_seqs, dtype=np.int32), np.diff(qsl)))
         if batch.feed_src is not None:
             self._put(self._feed, batch.feed_src)
+        if batch.rec_slots is not None:
+            self._put(self._rec_slots, batch.rec_slots)
         self._put(self._block_table, batch.block_table)
         self._put(self._seq_lens, batch.seq_lens)
         self._put(self._qsl, batch.query_start_loc)
@@ -383,6 +390,7 @@ class InputData:
         self._slots[1][b:bucket].fill_(dummy_slot)
         self._block_table[1][b:bucket, 0].fill_(dummy_page)
         self._seq_lens[1][b:bucket].fill_(1)
+        self._rec_slots[1][b:bucket].fill_(self.dummy_state_slot)
         self._qsl[1][b:bucket + 1].copy_(torch.arange(b, bucket + 1, dtype=torch.int32, device=self.device))
         self.padded_tokens = bucket
 
@@ -409,6 +417,9 @@ class InputData:
         if self.padded_tokens or self.num_decode_seqs == self.num_seqs:
             return None
         return self._tok_seq[1][: self.num_tokens]
+
+    @property
+    def rec_slots(self): return self._rec_slots[1][: self._n_seq()]
 
     @property
     def block_table(self): return self._block_table[1][: self._n_seq()]

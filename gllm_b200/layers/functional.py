@@ -103,3 +103,64 @@ def sample(logits, inp, seen_bits=None, seed=0, step=None):
     g = torch.Generator().manual_seed(seed + (int(step) if step is not None else 0))
     return ref.sample(logits, inp.temperature[:b], inp.top_k[:b], inp.top_p[:b],
                       inp.rep_penalty[:b] if seen_bits is not None else None, seen_mask, generator=g)
+
+
+# -- fp32-residual blocks, windowed sink attention, recurrent mixers (csrc/seq) ----------------------------
+def _seq():
+    from gllm_b200.ops import sm100_seq
+    return sm100_seq
+
+
+def linear_any(x, w):
+    """y = x @ w.T for bf16 or fp32 operands of any shape: the tcgen05 GEMM when it applies (bf16, 16-byte aligned
+    rows), else the plain fp32-accumulating kernel (true fp32 for fp32 operands, no TF32)."""
+    if x.is_cuda:
+        return _seq().linear_any(x, w)
+    return ref.linear(x, w)
+
+
+def embedding_scaled(ids, table, scale):
+    if table.is_cuda:
+        return _seq().embedding_scaled(ids, table, scale)
+    return ref.embedding_scaled(ids, table, scale)
+
+
+def resid_norm(x, y, w_post, add, w_pre, eps, out_dtype):
+    if x.is_cuda:
+        return _seq().resid_norm(x, y, w_post, add, w_pre, eps, out_dtype)
+    return ref.resid_norm(x, y, w_post, add, w_pre, eps, out_dtype)
+
+
+def qk_norm_kv_write(qk, num_heads, num_kv_heads, dim, q_norm_w, k_norm_w, eps, k_cache, v_cache, slots):
+    if qk.is_cuda:
+        return _seq().qk_norm_kv_write(qk, num_heads, num_kv_heads, dim, q_norm_w, k_norm_w, eps, k_cache, v_cache,
+                                       slots)
+    return ref.qk_norm_kv_write(qk, num_heads, num_kv_heads, dim, q_norm_w, k_norm_w, eps, k_cache, v_cache, slots)
+
+
+def window_attention(q, k_cache, v_cache, inp, scale, num_q_heads, head_dim, window, sink):
+    if q.is_cuda:
+        return _seq().window_attention(q, k_cache, v_cache, inp.block_table, inp.seq_lens, inp.query_start_loc,
+                                       inp.positions, scale, num_q_heads, head_dim, window, sink)
+    return ref.window_attention(q, k_cache, v_cache, inp.block_table, inp.seq_lens, inp.query_start_loc, scale,
+                                num_q_heads, head_dim, window, sink)
+
+
+def causal_conv_silu(xz, channels, w, b, conv_state, inp):
+    slots = inp.rec_slots if conv_state is not None else None
+    if xz.is_cuda:
+        return _seq().causal_conv_silu(xz, channels, w, b, conv_state, slots, inp.seq_lens, inp.query_start_loc)
+    return ref.causal_conv_silu(xz, channels, w, b, conv_state, slots, inp.seq_lens, inp.query_start_loc)
+
+
+def selective_scan(xc, dt_raw, proj, xz, a, d_skip, dt_bias, ssm_state, inp, channels, nstate, dt_rank):
+    slots = inp.rec_slots if ssm_state is not None else None
+    fn = _seq().selective_scan if xc.is_cuda else ref.selective_scan
+    return fn(xc, dt_raw, proj, xz, a, d_skip, dt_bias, ssm_state, slots, inp.seq_lens, inp.query_start_loc,
+              channels, nstate, dt_rank)
+
+
+def relu2(x):
+    if x.is_cuda:
+        return _seq().relu2(x)
+    return ref.relu2(x)

@@ -43,8 +43,56 @@ class KVCache:
         return 2 * num_layers * page_size * kv_head_num * kv_head_dim * dtype_bytes
 
 
+class HybridCache:
+    """Device storage for a model whose layers keep different things (models/hybrid.py): one entry per layer RUN
+    (a layer inside a weight-shared loop has one entry per pass). `layout[r]` is
+      {"kind": "kv", "heads", "dim"}                 -> k_cache[r], v_cache[r]: paged, same slab layout as `KVCache`
+      {"kind": "ssm", "channels", "nstate", "taps"}  -> conv_state[r] [slots, taps - 1, channels] (compute dtype) and
+                                                        ssm_state[r] [slots, nstate, channels] fp32, indexed by the
+                                                        sequence's state slot (`Sequence.rec_slot`)
+    Slot contents are never cleared on re-use: the kernels start from zeros for a chunk at position 0."""
+
+    def __init__(self, layout: List[dict], num_pages: int, page_size: int, num_slots: int, dtype: torch.dtype, device):
+        self.layout, self.num_pages, self.page_size, self.num_slots = layout, num_pages, page_size, num_slots
+        self.num_layers = len(layout)
+        self.use_mla = False
+        self.k_cache, self.v_cache, self.conv_state, self.ssm_state = [], [], [], []
+        for e in layout:
+            k = v = cs = ss = None
+            if e["kind"] == "kv":
+                shape = kv_cache_shape(num_pages, e["heads"], e["dim"], page_size)
+                k = torch.zeros(shape, dtype=dtype, device=device)
+                v = torch.zeros(shape, dtype=dtype, device=device)
+            elif e["kind"] == "ssm":
+                cs = torch.zeros(num_slots, max(e["taps"] - 1, 1), e["channels"], dtype=dtype, device=device)
+                ss = torch.zeros(num_slots, e["nstate"], e["channels"], dtype=torch.float32, device=device)
+            else:
+                raise ValueError(e["kind"])
+            self.k_cache.append(k)
+            self.v_cache.append(v)
+            self.conv_state.append(cs)
+            self.ssm_state.append(ss)
+
+    @staticmethod
+    def bytes_per_page(layout, page_size: int, dtype_bytes: int) -> int:
+        return sum(2 * page_size * e["heads"] * e["dim"] * dtype_bytes for e in layout if e["kind"] == "kv")
+
+    @staticmethod
+    def bytes_per_slot(layout, dtype_bytes: int) -> int:
+        return sum(max(e["taps"] - 1, 1) * e["channels"] * dtype_bytes + 4 * e["nstate"] * e["channels"]
+                   for e in layout if e["kind"] == "ssm")
+
+
 class MemoryManager:
-    def __init__(self, num_pages: int, page_size: int, reserve_dummy_page: bool = False):
+    def __init__(self, num_pages: int, page_size: int, reserve_dummy_page: bool = False, num_state_slots: int = 0):
+        # recurrent-state slots (models with slot-indexed per-sequence state): a sequence takes one when its first
+        # chunk is scheduled and gives it back together with its pages; the LAST slot absorbs CUDA-graph padding rows
+        self.num_state_slots = num_state_slots
+        self.state_alloc: Optional[IDAllocator] = None
+        if num_state_slots > 0:
+            self.state_alloc = IDAllocator(0, num_state_slots - 1)
+            if reserve_dummy_page:
+                self.state_alloc.allocate(num_state_slots - 1)
         self.num_pages = num_pages
         self.page_size = page_size
         self.id_allocator = IDAllocator(0, num_pages - 1)
@@ -67,7 +115,25 @@ class MemoryManager:
             for _ in range(self.pages_needed(seq)):
                 seq.page_table.append(self.allocate_page())
 
+    def acquire_state(self, seq: Sequence) -> bool:
+        """Give `seq` a recurrent-state slot if the model needs one; False when none is free right now."""
+        if self.state_alloc is None or seq.rec_slot >= 0:
+            return True
+        if self.state_alloc.get_num_free_ids() == 0:
+            return False
+        seq.rec_slot = self.state_alloc.allocate()
+        return True
+
+    def release_state(self, seq: Sequence):
+        if self.state_alloc is not None and seq.rec_slot >= 0:
+            self.state_alloc.free(seq.rec_slot)
+        seq.rec_slot = -1
+
+    def get_num_free_state_slots(self) -> int:
+        return self.state_alloc.get_num_free_ids() if self.state_alloc is not None else 1 << 30
+
     def free(self, seq: Sequence):
+        self.release_state(seq)
         for page in seq.page_table:
             self.free_page(page)
         seq.page_table = []
@@ -96,7 +162,8 @@ class MemoryManager:
 class PrefixMemoryManager(MemoryManager):
     """Adds a hash -> page map with reference counts (automatic prefix caching)."""
 
-    def __init__(self, num_pages: int, page_size: int, reserve_dummy_page: bool = False):
+    def __init__(self, num_pages: int, page_size: int, reserve_dummy_page: bool = False, num_state_slots: int = 0):
+        assert num_state_slots == 0, "a page-hash prefix cache cannot restore recurrent state"
         super().__init__(num_pages, page_size, reserve_dummy_page)
         self.hash2page: Dict[int, int] = {}
         self.page2hash: List[Optional[int]] = [None] * num_pages

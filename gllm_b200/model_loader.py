@@ -19,10 +19,14 @@ from gllm_b200.utils.logging import logger
 
 
 class ModelLoader:
-    def __init__(self, model_path, load_format: str = "auto"):
+    def __init__(self, model_path, load_format: str = "auto", dtype: Optional[str] = None):
         self.model_path = model_path
         self.load_format = load_format
         self.config = self.load_config(model_path)
+        if "architectures" not in self.config and "architecture" in self.config:
+            self.config["architectures"] = [self.config["architecture"]]   # single-name form of the key
+        if dtype is not None:
+            self.config["torch_dtype"] = dtype
         self.generation_config = self.load_generation_config(model_path)
         self.architecture = self.config["architectures"][0]
         self.use_mla = self.architecture in ("DeepseekV2ForCausalLM", "DeepseekV3ForCausalLM") and \

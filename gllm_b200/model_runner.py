@@ -22,7 +22,7 @@ import torch
 from gllm_b200.config import EngineConfig, capture_sizes
 from gllm_b200.input_data import BatchArrays, InputData
 from gllm_b200.layers import functional as Fn
-from gllm_b200.memory_manager import KVCache
+from gllm_b200.memory_manager import HybridCache, KVCache
 from gllm_b200.model_loader import ModelLoader
 from gllm_b200.parallel import state as ps
 from gllm_b200.parallel.tp import make_tp_comm
@@ -50,7 +50,7 @@ class StepResult:
 class ModelRunner:
     def __init__(self, cfg: EngineConfig, loader: Optional[ModelLoader] = None):
         self.cfg = cfg
-        self.loader = loader or ModelLoader(cfg.model_path, cfg.load_format)
+        self.loader = loader or ModelLoader(cfg.model_path, cfg.load_format, dtype=cfg.dtype)
         self.page_size = cfg.page_size
         self.max_num_batched_tokens = cfg.max_num_batched_tokens
         self.max_running_seqs = cfg.max_running_seqs
@@ -91,6 +91,11 @@ class ModelRunner:
         t0 = time.time()
         self.model = self.loader.load_model(self.device, progress)
         self.spec = self.model.spec
+        self.hybrid = bool(getattr(self.model, "is_hybrid", False))   # per-layer cache layout + recurrent-state slots
+        self.num_state_slots = 0
+        if self.hybrid and self.model.has_state:
+            # one slot per running sequence + the padding slot; the scheduler admits a sequence only with a slot
+            self.num_state_slots = (cfg.num_state_slots or min(max(self.max_running_seqs, 1), 256)) + 1
         want_fused = cfg.tp_mode == "fused" and cfg.tp_size > 1 and is_cuda
         why_not = "fp8 block-scaled linears" if getattr(self.spec, "quant", None) is not None else \
             "DeepStack (Qwen3-VL) feature injection" if getattr(self.model, "num_deepstack", 0) else None
@@ -129,9 +134,14 @@ class ModelRunner:
         logger.info("model loaded in %.1fs", time.time() - t0)
         self.profile_run()
         self.num_pages = self.compute_num_pages()
-        kvh, kvd = self.kv_shape()
-        self.kv_cache = KVCache(self.model.num_layers, self.num_pages, self.page_size, kvh, kvd, dt, self.device,
-                                use_mla=self.loader.use_mla)
+        if self.hybrid:
+            self.kv_cache = HybridCache(self.model.cache_layout(), self.num_pages, self.page_size,
+                                        self.num_state_slots, dt, self.device)
+            self.input_data.dummy_state_slot = max(self.num_state_slots - 1, 0)
+        else:
+            kvh, kvd = self.kv_shape()
+            self.kv_cache = KVCache(self.model.num_layers, self.num_pages, self.page_size, kvh, kvd, dt, self.device,
+                                    use_mla=self.loader.use_mla)
         if is_cuda and not cfg.disable_cuda_graph:
             self.capture_graphs()
         return self
@@ -157,6 +167,8 @@ class ModelRunner:
 
     def compute_num_pages(self) -> int:
         cfg = self.cfg
+        if self.hybrid:
+            return self._hybrid_num_pages()
         kvh, kvd = self.kv_shape()
         per_page = KVCache.bytes_per_page(self.model.num_layers, self.page_size, kvh, kvd,
                                           torch.empty(0, dtype=self.spec.dtype).element_size(), self.loader.use_mla)
@@ -176,6 +188,42 @@ class ModelRunner:
                     per_page / 1024 / self.page_size, num * per_page / 2 ** 30)
         assert num >= 4, "not enough memory for the KV cache"
         return num
+
+    def _hybrid_num_pages(self) -> int:
+        cfg = self.cfg
+        layout = self.model.cache_layout()
+        esz = torch.empty(0, dtype=self.spec.dtype).element_size()
+        per_page = HybridCache.bytes_per_page(layout, self.page_size, esz)
+        state = HybridCache.bytes_per_slot(layout, esz) * self.num_state_slots
+        if self.device.type != "cuda":
+            num = cfg.num_cpu_pages
+        elif cfg.num_gpu_pages is not None:
+            num = cfg.num_gpu_pages
+        elif per_page == 0:
+            num = 4
+        else:
+            torch.cuda.empty_cache()
+            free, _ = torch.cuda.mem_get_info(self.device)
+            num = int(((free - state) // per_page) * cfg.gpu_memory_util)
+        if not self.model.has_pages:
+            # no paged layer: pages only count positions; enough of them that they never limit admission
+            num = max(num, (self.num_state_slots * self.model_max_length) // self.page_size + 8)
+        logger.info("cache: %d pages (%d tokens/page, %.2f KB/token), %d state slots (%.2f MB each)", num,
+                    self.page_size, per_page / 1024 / self.page_size, self.num_state_slots,
+                    HybridCache.bytes_per_slot(layout, esz) / 2 ** 20)
+        assert num >= 4, "not enough memory for the cache"
+        return num
+
+    def step_logits(self, batch: BatchArrays) -> torch.Tensor:
+        """One eager step that returns fp32 logits [len(batch.logits_idx), V] instead of sampling (logit tracing,
+        numerics checks). `batch.logits_idx` may name any rows of the batch."""
+        self.stats["steps"] += 1
+        self.stats["tokens"] += batch.num_tokens
+        if batch.logits_idx.shape[0] == 0:
+            batch.logits_idx = np.zeros(1, np.int32)
+            return self._forward(batch, None, None)[0][:0, : self.spec.vocab_size].float()
+        out, _ = self._forward(batch, None, None)
+        return out[:, : self.spec.vocab_size].float()
 
     # -------------------------------------------------------------------------------------------
     def _forward(self, batch: BatchArrays, hidden, residual, use_kv=True):
@@ -202,17 +250,23 @@ class ModelRunner:
         self.graph_logits: Dict[int, torch.Tensor] = {}
         self.graph_hidden: Dict[int, tuple] = {}
         from gllm_b200.ops import sm100
-        kvh, _ = self.kv_shape()
-        sm100.reserve_attn_workspace(self.device, max(self.capture_sizes or [1]), self.model.layers[0].attn.num_heads
-                                     if len(self.model.layers) else 1, self.model.head_dim)
+        if not self.hybrid:
+            kvh, _ = self.kv_shape()
+            sm100.reserve_attn_workspace(self.device, max(self.capture_sizes or [1]),
+                                         self.model.layers[0].attn.num_heads if len(self.model.layers) else 1,
+                                         self.model.head_dim)
         dummy_page = self.num_pages - 1
         t0 = time.time()
         for bs in self.capture_sizes:
             batch = _dummy_batch(bs, bs, self.page_size, inp.max_blocks, page=dummy_page, decode=True)
             inp.load(batch)
             inp.padded_tokens = bs
-            inp.decode_splits = sm100.decode_splits(bs, max(kvh, 1), self.model.layers[0].attn.num_heads
-                                                    if len(self.model.layers) else 1, self.model_max_length)
+            if batch.rec_slots is None and self.num_state_slots:
+                batch.rec_slots = np.full(bs, self.num_state_slots - 1, np.int32)
+                inp.load(batch)
+            inp.decode_splits = None if self.hybrid else sm100.decode_splits(
+                bs, max(kvh, 1), self.model.layers[0].attn.num_heads if len(self.model.layers) else 1,
+                self.model_max_length)
             hid = res = None
             if not ps.is_first_pp_rank():
                 hid, res = self.input_hidden[:bs], self.input_residual[:bs]

@@ -1,0 +1,262 @@
+"""Layer-list decoder: a stack whose every layer names its own mixer (windowed sink attention, Mamba-1 scan) and
+an optional feed-forward, with sandwich norms around each sublayer, an fp32 residual stream and an optional loop
+that re-runs a span of layers with shared weights. Architecture `Saritar` is built from it.
+
+    x = embed[token] * embed_scale                                   (fp32 from here on)
+    per layer:  x += rms(mixer(rms(x) * n1)) * n1b ;  x += rms(ff(rms(x) * n2)) * n2b   (second line only with a ff)
+    loop (start, stop, times): layers start..stop-1 run `times` times back to back; every pass has its own cache
+        entries ("layer runs"), and before each pass but the first the embedding output is added to x
+    logits = head @ (rms(x) * final_norm)
+
+Dataflow on the device: every residual update is ONE kernel that applies the post-norm, adds into the fp32 stream,
+optionally adds the embedding (loop re-entry) and emits the next sublayer's pre-normed input in the compute dtype
+(`Fn.resid_norm`), so the stream is read and written once per sublayer.
+
+config.json keys read here: architecture, vocab, width, embedding.scale, norm.eps, loop.{start,stop,times},
+layers[i].{type, mixer{...}, mlp{kind, ff} | null}, optional torch_dtype. Tensor names: embed, head, final.norm,
+l<i>.norm1|norm1b|norm2|norm2b, l<i>.mix.*, l<i>.mlp.up|down.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Callable, List, Optional
+
+import torch
+from torch import nn
+
+from gllm_b200.layers import functional as Fn
+from gllm_b200.layers.ssm import Mamba1Mixer
+from gllm_b200.layers.window_attention import SinkWindowAttention
+from gllm_b200.parallel import state as ps
+
+_DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32, torch.bfloat16: torch.bfloat16,
+           torch.float32: torch.float32}
+
+
+@dataclass
+class HybridSpec:
+    arch: str
+    hidden_size: int
+    vocab_size: int
+    rms_eps: float
+    embed_scale: float
+    layers: List[dict]
+    loop_start: int = 0
+    loop_stop: int = 0
+    loop_times: int = 1
+    dtype: torch.dtype = torch.bfloat16
+    eos_token_id: Optional[object] = None
+    use_mla: bool = False
+    quant: Optional[str] = None
+    extra: dict = field(default_factory=dict)
+
+    @property
+    def num_layers(self) -> int:
+        return len(self.layers)
+
+
+def spec_saritar(cfg) -> HybridSpec:
+    loop = cfg.get("loop") or {}
+    dt = cfg.get("torch_dtype", cfg.get("dtype", "bfloat16"))
+    if dt not in _DTYPES:
+        raise ValueError(f"unsupported dtype {dt} for this architecture (bfloat16 | float32)")
+    return HybridSpec(arch="saritar", hidden_size=int(cfg["width"]), vocab_size=int(cfg["vocab"]),
+                      rms_eps=float(cfg["norm"]["eps"]), embed_scale=float((cfg.get("embedding") or {}).get("scale", 1.0)),
+                      layers=[dict(x) for x in cfg["layers"]], loop_start=int(loop.get("start", 0)),
+                      loop_stop=int(loop.get("stop", 0)), loop_times=int(loop.get("times", 1)), dtype=_DTYPES[dt],
+                      eos_token_id=cfg.get("eos_token_id"))
+
+
+def layer_runs(n_layers: int, start: int, stop: int, times: int):
+    """[(layer index, add_embed)] in execution order; add_embed marks the first layer of every pass but the first."""
+    if times <= 1 or stop <= start:
+        return [(i, False) for i in range(n_layers)]
+    runs = [(i, False) for i in range(start)]
+    for r in range(times):
+        runs += [(i, r > 0 and i == start) for i in range(start, stop)]
+    return runs + [(i, False) for i in range(stop, n_layers)]
+
+
+class Relu2MLP(nn.Module):
+    """down(relu(up(h))^2)"""
+
+    def __init__(self, hidden: int, ff: int, dtype, device):
+        super().__init__()
+        self.up_w = nn.Parameter(torch.zeros(ff, hidden, dtype=dtype, device=device), requires_grad=False)
+        self.down_w = nn.Parameter(torch.zeros(hidden, ff, dtype=dtype, device=device), requires_grad=False)
+
+    def forward(self, h):
+        return Fn.linear_any(Fn.relu2(Fn.linear_any(h, self.up_w)), self.down_w)
+
+
+def make_mixer(kind: str, m: dict, spec: HybridSpec, device):
+    h, dt = spec.hidden_size, spec.dtype
+    if kind == "attention":
+        assert int(m.get("vdim", m["dim"])) == int(m["dim"]), "values are the keys: vdim must equal dim"
+        window = (m.get("mask") or {}).get("size")
+        return SinkWindowAttention(h, int(m["heads"]), int(m["kv_heads"]), int(m["dim"]), float(m["scale"]),
+                                   int(window) if window is not None else None, spec.rms_eps, dt, device)
+    if kind == "mamba1":
+        return Mamba1Mixer(h, int(m["inner"]), int(m["state"]), int(m["dt_rank"]), int(m["conv"]), dt, device)
+    raise ValueError(f"unknown mixer type {kind!r}")
+
+
+class HybridLayer(nn.Module):
+    def __init__(self, spec: HybridSpec, layer_id: int, device):
+        super().__init__()
+        L = spec.layers[layer_id]
+        h, dt = spec.hidden_size, spec.dtype
+
+        def norm():
+            return nn.Parameter(torch.ones(h, dtype=dt, device=device), requires_grad=False)
+
+        self.layer_id = layer_id
+        self.kind = L["type"]
+        self.norm1_w, self.norm1b_w = norm(), norm()
+        self.mixer = make_mixer(L["type"], L["mixer"], spec, device)
+        mlp = L.get("mlp")
+        if mlp is not None:
+            if mlp.get("kind", "dense") != "dense":
+                raise ValueError(f"unknown feed-forward kind {mlp.get('kind')!r}")
+            self.norm2_w, self.norm2b_w = norm(), norm()
+            self.mlp = Relu2MLP(h, int(mlp["ff"]), dt, device)
+        else:
+            self.mlp = None
+
+
+class HybridLM(nn.Module):
+    ret_residual = False
+    is_hybrid = True
+
+    def __init__(self, spec: HybridSpec, device="cpu"):
+        super().__init__()
+        assert ps.get_world_size() == 1, "layer-list decoders run on one GPU (no TP / PP sharding yet)"
+        self.spec = spec
+        self.device = torch.device(device)
+        h, dt = spec.hidden_size, spec.dtype
+        self.embed_w = nn.Parameter(torch.zeros(spec.vocab_size, h, dtype=dt, device=device), requires_grad=False)
+        self.layers = nn.ModuleList([HybridLayer(spec, i, device) for i in range(spec.num_layers)])
+        self.final_norm_w = nn.Parameter(torch.ones(h, dtype=dt, device=device), requires_grad=False)
+        self.lm_head_w = nn.Parameter(torch.zeros(spec.vocab_size, h, dtype=dt, device=device), requires_grad=False)
+        self.runs = layer_runs(spec.num_layers, spec.loop_start, spec.loop_stop, spec.loop_times)
+        self.has_state = any(not l.mixer.uses_pages for l in self.layers)
+        self.has_pages = any(l.mixer.uses_pages for l in self.layers)
+        self.trace: Optional[list] = None     # debugging: when a list, the stream after every layer run is appended
+
+    # -- what the runner asks ---------------------------------------------------------------------
+    @property
+    def num_layers(self): return len(self.runs)
+
+    @property
+    def hidden_size(self): return self.spec.hidden_size
+
+    def cache_layout(self):
+        """One entry per layer RUN (a looped layer has one per pass)."""
+        return [self.layers[i].mixer.cache_entry() for i, _ in self.runs]
+
+    # -- forward ----------------------------------------------------------------------------------
+    def forward(self, inp, cache, tpc=None, hidden=None, residual=None, **_):
+        spec, eps, dt = self.spec, self.spec.rms_eps, self.spec.dtype
+        x0 = Fn.embedding_scaled(inp.tokens, self.embed_w, spec.embed_scale)
+        x = x0.clone() if any(a for _, a in self.runs) else x0
+        n = len(self.runs)
+        h = Fn.resid_norm(x, None, None, None, self.layers[self.runs[0][0]].norm1_w if n else self.final_norm_w,
+                          eps, dt)
+        for r, (li, _) in enumerate(self.runs):
+            L = self.layers[li]
+            y = L.mixer(inp, h, cache, r)
+            post = L.norm1b_w
+            if L.mlp is not None:
+                h = Fn.resid_norm(x, y, post, None, L.norm2_w, eps, dt)
+                y = L.mlp(h)
+                post = L.norm2b_w
+            last = r + 1 == n
+            w_pre = self.final_norm_w if last else self.layers[self.runs[r + 1][0]].norm1_w
+            add = x0 if (not last and self.runs[r + 1][1]) else None
+            if self.trace is not None:
+                Fn.resid_norm(x, y, post, None, None, eps, dt)
+                self.trace.append(x.clone())
+                h = Fn.resid_norm(x, None, None, add, w_pre, eps, dt)
+            else:
+                h = Fn.resid_norm(x, y, post, add, w_pre, eps, dt)
+        return h, None
+
+    def compute_logits(self, inp, hidden, tpc=None, all_rows: bool = False, local: bool = False):
+        rows = hidden if all_rows else hidden.index_select(0, inp.logits_idx.long())
+        return Fn.linear_any(rows, self.lm_head_w)
+
+    # -- weights ----------------------------------------------------------------------------------
+    def process_weights(self):
+        pass
+
+    def init_dummy(self, seed: int = 0):
+        g = torch.Generator(device="cpu").manual_seed(seed)
+
+        def rnd(p, std):
+            p.data.copy_((torch.randn(p.shape, generator=g) * std).to(p.dtype))
+
+        for name, p in self.named_parameters():
+            if name.endswith("norm_w") or "norm1" in name or "norm2" in name:
+                p.data.fill_(1.0)
+            elif name.endswith(".a"):
+                p.data.copy_(-torch.exp(torch.rand(p.shape, generator=g) * 2.0 - 1.0))
+            elif name.endswith("dt_b"):
+                p.data.copy_(torch.rand(p.shape, generator=g) * 2.0 - 3.0)
+            elif name.endswith("d_skip"):
+                p.data.fill_(1.0)
+            elif name.endswith("sink") or name.endswith("conv_b"):
+                rnd(p, 0.5)
+            elif name.endswith("conv_w"):
+                rnd(p, 0.4)
+            elif p.dim() == 2:
+                rnd(p, 1.0 / max(p.shape[1], 1) ** 0.5)
+            else:
+                rnd(p, 0.02)
+
+    def load_weights(self, reader, progress: Optional[Callable[[int, int], None]] = None):
+        total = len(self.layers) + 2
+
+        def put(param, t):
+            assert tuple(param.shape) == tuple(t.shape), (tuple(param.shape), tuple(t.shape))
+            param.data.copy_(t)
+
+        put(self.embed_w, reader.get("embed"))
+        for n, L in enumerate(self.layers):
+            pre = f"l{L.layer_id}."
+            put(L.norm1_w, reader.get(pre + "norm1"))
+            put(L.norm1b_w, reader.get(pre + "norm1b"))
+            m = L.mixer
+            mp = pre + "mix."
+            if isinstance(m, SinkWindowAttention):
+                put(m.qk_w, torch.cat([reader.get(mp + "q"), reader.get(mp + "k")], 0))
+                if m.q_norm_w is not None:
+                    put(m.q_norm_w, reader.get(mp + "q.norm"))
+                    put(m.k_norm_w, reader.get(mp + "k.norm"))
+                if m.sink is not None:
+                    put(m.sink, reader.get(mp + "sink").float())
+                put(m.o_w, reader.get(mp + "o"))
+            elif isinstance(m, Mamba1Mixer):
+                put(m.in_w, reader.get(mp + "in"))
+                put(m.conv_w, reader.get(mp + "conv").float())
+                put(m.conv_b, reader.get(mp + "conv.b").float())
+                put(m.x_w, reader.get(mp + "x"))
+                put(m.dt_w, reader.get(mp + "dt"))
+                put(m.dt_b, reader.get(mp + "dt.b").float())
+                put(m.a, -torch.exp(reader.get(mp + "A_log").float()))
+                put(m.d_skip, reader.get(mp + "D").float())
+                put(m.o_w, reader.get(mp + "o"))
+            if L.mlp is not None:
+                put(L.norm2_w, reader.get(pre + "norm2"))
+                put(L.norm2b_w, reader.get(pre + "norm2b"))
+                put(L.mlp.up_w, reader.get(pre + "mlp.up"))
+                put(L.mlp.down_w, reader.get(pre + "mlp.down"))
+            if progress is not None:
+                progress(n + 2, total)
+        put(self.final_norm_w, reader.get("final.norm"))
+        put(self.lm_head_w, reader.get("head"))
+        if progress is not None:
+            progress(total, total)
+
+
+def build_saritar(cfg, device):
+    return HybridLM(spec_saritar(cfg), device)

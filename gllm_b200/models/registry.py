@@ -4,7 +4,7 @@ Supported `architectures[0]` values:
   LlamaForCausalLM, Qwen2ForCausalLM, Qwen3ForCausalLM, Qwen2MoeForCausalLM, Qwen3MoeForCausalLM,
   MixtralForCausalLM, ChatGLMModel / ChatGLMForConditionalGeneration, DeepseekV2ForCausalLM,
   DeepseekV3ForCausalLM, Qwen2_5_VLForConditionalGeneration, Qwen3VLForConditionalGeneration,
-  Qwen3VLMoeForConditionalGeneration.
+  Qwen3VLMoeForConditionalGeneration, Saritar (layer-list decoder, models/hybrid.py).
 """
 from __future__ import annotations
 
@@ -161,7 +161,13 @@ def _build_qwen3_vl(cfg, device):
     return build_qwen3_vl(cfg, device)
 
 
+def _build_saritar(cfg, device):
+    from gllm_b200.models.hybrid import build_saritar
+    return build_saritar(cfg, device)
+
+
 ARCHITECTURES: Dict[str, Callable] = {
+    "Saritar": _build_saritar,
     "LlamaForCausalLM": _build_decoder(spec_llama),
     "MistralForCausalLM": _build_decoder(spec_llama),
     "Qwen2ForCausalLM": _build_decoder(spec_qwen2),

@@ -452,3 +452,152 @@ def merge_attn_states(o1: torch.Tensor, lse1: torch.Tensor, o2: torch.Tensor, ls
     den = w1 + w2
     o = (o1.float() * (w1 / den).unsqueeze(-1) + o2.float() * (w2 / den).unsqueeze(-1)).to(o1.dtype)
     return o, m + torch.log(den)
+
+
+# ----------------------------------------------------------------------------------------------
+# fp32-residual blocks, windowed attention with a sink, short convolution + selective scan
+# (unfused PyTorch forms of csrc/seq/*.cu; the CPU engine path and the kernels' numerics oracle)
+# ----------------------------------------------------------------------------------------------
+def embedding_scaled(ids: torch.Tensor, table: torch.Tensor, scale: float) -> torch.Tensor:
+    """fp32 residual stream from token ids: table[id] * scale."""
+    return table[ids.long()].float() * scale
+
+
+def resid_norm(x: torch.Tensor, y: Optional[torch.Tensor], w_post: Optional[torch.Tensor],
+               add: Optional[torch.Tensor], w_pre: Optional[torch.Tensor], eps: float, out_dtype):
+    """In place on the fp32 stream x [T, W]:  x += rms(y) * w_post ;  x += add ;  returns rms(x) * w_pre cast to
+    `out_dtype` (None when w_pre is None). Every step is optional. All arithmetic in fp32."""
+    if y is not None:
+        yf = y.float()
+        x += yf * torch.rsqrt((yf * yf).mean(-1, keepdim=True) + eps) * w_post.float()
+    if add is not None:
+        x += add
+    if w_pre is None:
+        return None
+    return (x * torch.rsqrt((x * x).mean(-1, keepdim=True) + eps) * w_pre.float()).to(out_dtype)
+
+
+def _cache_rows_write(cache: torch.Tensor, slots: torch.Tensor, rows: torch.Tensor):
+    """rows [T, Hkv, D] -> paged cache [pages, Hkv, D/w, page_size, w] at flat slots (negative slots skipped)."""
+    ps, w = cache.shape[3], cache.shape[4]
+    keep = slots >= 0
+    s = slots[keep].long()
+    r = rows[keep]
+    cache[s // ps, :, :, s % ps, :] = r.reshape(r.shape[0], r.shape[1], -1, w).to(cache.dtype)
+
+
+def qk_norm_kv_write(qk: torch.Tensor, num_heads: int, num_kv_heads: int, dim: int, q_norm_w, k_norm_w, eps: float,
+                     k_cache: torch.Tensor, v_cache: torch.Tensor, slots: torch.Tensor) -> torch.Tensor:
+    """qk [T, (H + G) * D] = [queries | keys]. Per-head RMS norm of q and k (weights optional); the normed key goes
+    to the K cache, the key as projected to the V cache (the values of this attention are its raw keys).
+    Returns the normed queries [T, H * D]."""
+    t = qk.shape[0]
+    q = qk[:, : num_heads * dim].reshape(t, num_heads, dim).float()
+    k = qk[:, num_heads * dim:].reshape(t, num_kv_heads, dim).float()
+    kn = k
+    if q_norm_w is not None:
+        q = q * torch.rsqrt((q * q).mean(-1, keepdim=True) + eps) * q_norm_w.float()
+    if k_norm_w is not None:
+        kn = k * torch.rsqrt((k * k).mean(-1, keepdim=True) + eps) * k_norm_w.float()
+    _cache_rows_write(k_cache, slots, kn.to(qk.dtype))
+    _cache_rows_write(v_cache, slots, k.to(qk.dtype))
+    return q.to(qk.dtype).reshape(t, num_heads * dim)
+
+
+def window_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
+                     seq_lens: torch.Tensor, query_start_loc: torch.Tensor, scale: float, num_q_heads: int,
+                     head_dim: int, window: Optional[int], sink: Optional[torch.Tensor]) -> torch.Tensor:
+    """Causal paged attention where position i sees j with 0 <= i - j < window (None: all of the past) and the
+    softmax denominator has one more term exp(sink[h]) that carries no value (None: plain softmax)."""
+    t = q.shape[0]
+    hq, d = num_q_heads, head_dim
+    g = hq // k_cache.shape[1]
+    out = torch.zeros(t, hq * d, dtype=q.dtype, device=q.device)
+    qsl, sl = query_start_loc.tolist(), seq_lens.tolist()
+    for s in range(len(sl)):
+        q0, q1 = qsl[s], qsl[s + 1]
+        ql = q1 - q0
+        if ql <= 0:
+            continue
+        kk = gather_kv(k_cache, block_table[s], sl[s]).float().repeat_interleave(g, dim=1)
+        vv = gather_kv(v_cache, block_table[s], sl[s]).float().repeat_interleave(g, dim=1)
+        qq = q[q0:q1].reshape(ql, hq, d).float()
+        att = torch.einsum("qhd,khd->hqk", qq, kk) * scale
+        qi = torch.arange(ql, device=q.device).view(ql, 1) + (sl[s] - ql)
+        kj = torch.arange(sl[s], device=q.device).view(1, sl[s])
+        dead = kj > qi
+        if window is not None:
+            dead = dead | (qi - kj >= window)
+        att = att.masked_fill(dead.unsqueeze(0), float("-inf"))
+        if sink is not None:
+            att = torch.cat([att, sink.float().view(hq, 1, 1).expand(hq, ql, 1)], dim=-1)
+        p = torch.softmax(att, dim=-1)[..., : sl[s]]
+        out[q0:q1] = torch.einsum("hqk,khd->qhd", p, vv).reshape(ql, hq * d).to(q.dtype)
+    return out
+
+
+def causal_conv_silu(xz: torch.Tensor, channels: int, w: torch.Tensor, b: torch.Tensor,
+                     conv_state: Optional[torch.Tensor], rec_slots: Optional[torch.Tensor], seq_lens: torch.Tensor,
+                     query_start_loc: torch.Tensor) -> torch.Tensor:
+    """Depthwise causal convolution + SiLU over the first `channels` columns of xz [T, >= channels], per sequence.
+    w [channels, taps] (last tap = current token), b [channels]. conv_state [slots, taps - 1, channels] holds the
+    last taps - 1 inputs of every sequence; a sequence whose chunk starts at position 0 starts from zeros."""
+    taps = w.shape[1]
+    out = torch.empty(xz.shape[0], channels, dtype=xz.dtype, device=xz.device)
+    qsl, sl = query_start_loc.tolist(), seq_lens.tolist()
+    for s in range(len(sl)):
+        q0, q1 = qsl[s], qsl[s + 1]
+        n = q1 - q0
+        if n <= 0:
+            continue
+        x = xz[q0:q1, :channels].float()
+        hist = torch.zeros(taps - 1, channels, dtype=torch.float32, device=xz.device)
+        if conv_state is not None and sl[s] - n > 0:
+            hist = conv_state[int(rec_slots[s])].float()
+        xp = torch.cat([hist, x], 0)
+        acc = b.float().expand(n, channels).clone()
+        for j in range(taps):
+            acc = acc + xp[j:j + n] * w[:, j].float()
+        out[q0:q1] = F.silu(acc).to(xz.dtype)
+        if conv_state is not None and taps > 1:
+            conv_state[int(rec_slots[s])] = xp[n:].to(conv_state.dtype)
+    return out
+
+
+def selective_scan(xc: torch.Tensor, dt_raw: torch.Tensor, proj: torch.Tensor, xz: torch.Tensor, a: torch.Tensor,
+                   d_skip: torch.Tensor, dt_bias: torch.Tensor, ssm_state: Optional[torch.Tensor],
+                   rec_slots: Optional[torch.Tensor], seq_lens: torch.Tensor, query_start_loc: torch.Tensor,
+                   channels: int, nstate: int, dt_rank: int) -> torch.Tensor:
+    """Selective state-space recurrence, fp32, token by token:
+        dt = softplus(dt_raw + dt_bias);  S <- exp(dt * A) * S + dt * x * B;  y = S . C + D * x;  out = y * silu(z)
+    xc [T, C] conv output, dt_raw [T, C], proj [T, R + 2N] = [.. | B | C], xz [T, 2C] = [.. | z], a [C, N] (negative),
+    ssm_state [slots, N, C] fp32 carried between chunks (zeros for a chunk that starts at position 0)."""
+    out = torch.empty(xc.shape[0], channels, dtype=xc.dtype, device=xc.device)
+    qsl, sl = query_start_loc.tolist(), seq_lens.tolist()
+    af = a.float()
+    for s in range(len(sl)):
+        q0, q1 = qsl[s], qsl[s + 1]
+        n = q1 - q0
+        if n <= 0:
+            continue
+        st = torch.zeros(channels, nstate, dtype=torch.float32, device=xc.device)
+        if ssm_state is not None and sl[s] - n > 0:
+            st = ssm_state[int(rec_slots[s])].t().clone()
+        dt = F.softplus(dt_raw[q0:q1].float() + dt_bias.float())
+        x = xc[q0:q1].float()
+        bm = proj[q0:q1, dt_rank:dt_rank + nstate].float()
+        cm = proj[q0:q1, dt_rank + nstate:dt_rank + 2 * nstate].float()
+        z = xz[q0:q1, channels:2 * channels].float()
+        ys = torch.empty(n, channels, dtype=torch.float32, device=xc.device)
+        for i in range(n):
+            st = torch.exp(dt[i].unsqueeze(1) * af) * st + (dt[i] * x[i]).unsqueeze(1) * bm[i].unsqueeze(0)
+            ys[i] = st @ cm[i] + d_skip.float() * x[i]
+        out[q0:q1] = (ys * F.silu(z)).to(xc.dtype)
+        if ssm_state is not None:
+            ssm_state[int(rec_slots[s])] = st.t()
+    return out
+
+
+def relu2(x: torch.Tensor) -> torch.Tensor:
+    r = torch.relu(x.float())
+    return (r * r).to(x.dtype)

@@ -314,6 +314,33 @@ class Scheduler:
         self.abort_ids &= live
         return out if out.free_ids else None
 
+    # -- replay: the caller decides what runs ----------------------------------------------------
+    def schedule_explicit(self, plan) -> List["ScheduledSeq"]:
+        """`plan` = [(seq, n)]: run the next n known tokens of each sequence as ONE micro-batch (trace replay,
+        numerics tests). Pages and recurrent-state slots come from the same managers as in policy scheduling and the
+        batch keeps the engine's row order (decode rows first); raises if the pool cannot hold the step."""
+        entries = []
+        for seq, n in plan:
+            if not self.mm.acquire_state(seq):
+                raise RuntimeError("no recurrent-state slot free for sequence %d" % seq.seq_id)
+            start = seq.scheduled_token_num
+            assert n >= 1 and start + n <= len(seq.token_ids), (start, n, len(seq.token_ids))
+            seq.scheduled_token_num = start + n
+            if self.mm.pages_needed(seq) > self.mm.get_num_free_pages():
+                raise RuntimeError("cache pool too small for sequence %d" % seq.seq_id)
+            self.mm.pre_allocate_page([seq])
+            entries.append(ScheduledSeq(seq, start, n))
+        entries.sort(key=lambda e: not e.is_decode)      # stable: decode rows first, order otherwise kept
+        self.batch_running.append(entries)
+        return entries
+
+    def complete_explicit(self, finished=()):
+        """The micro-batch queued by `schedule_explicit` has run; `finished` sequences give back what they hold."""
+        for ent in self.batch_running.popleft():
+            ent.seq.computed_token_num = max(ent.seq.computed_token_num, ent.start + ent.n)
+        for seq in finished:
+            self.mm.free(seq)
+
     # -- scheduling -------------------------------------------------------------------------------
     def can_schedule(self) -> bool:
         return bool(self.seqs_to_decode or self.seqs_to_prefill) and len(self.batch_running) < self.pp_size
@@ -394,6 +421,8 @@ class Scheduler:
             seq = self.seqs_to_prefill[0]
             if isinstance(self.mm, PrefixMemoryManager) and seq.scheduled_token_num == 0 and not seq.page_table:
                 self.mm.pre_allocate_computed_page([seq])
+            if not self.mm.acquire_state(seq):
+                break  # every recurrent-state slot is held by a running sequence
             start = seq.scheduled_token_num
             remaining = len(seq) - start
             take = min(remaining, budget)

@@ -10,7 +10,7 @@ class Sequence:
                  "repetition_penalty", "computed_token_num", "scheduled_token_num", "is_abort",
                  "mm_contents", "page_hashes", "num_cached_tokens", "arrival_time", "first_token_time",
                  "finish_time", "slot", "mrope_delta", "mm_state", "pt_np", "pending", "zombie", "pt_gen", "published",
-                 "slot_fresh")
+                 "slot_fresh", "rec_slot")
 
     def __init__(self, seq_id: int, token_ids: List[int], finish_tokens: List[int],
                  output_len: Optional[int] = None, ignore_eos: bool = False, temperature: float = 0.6,
@@ -43,6 +43,7 @@ class Sequence:
         self.finish_time = 0.0
         self.published = 0   # leading pages of page_table already offered to the prefix cache
         self.slot_fresh = False  # penalty state row just (re)assigned: rebuild its contents at the next emission
+        self.rec_slot = -1  # recurrent-state slot (models with per-sequence state), -1: none held
         self.slot = -1  # row in the persistent per-sequence device state (penalty bitmask, ...)
         self.mrope_delta = 0
         self.pt_np = None  # numpy mirror of page_table (rebuilt only when its length changes)
