@@ -86,7 +86,11 @@ def build(force: bool = False, verbose: bool = False) -> str:
 
     def compile_one(item):
         s, obj, dig, digf = item
-        cmd = [nvcc_path(), *NVCC_FLAGS, "-I", CSRC, "-c", s, "-o", obj]
+        flags = NVCC_FLAGS
+        if os.sep + "seq" + os.sep in s:
+            # recurrences, softplus and decays there are specified in accurate fp32: no approximate intrinsics
+            flags = [f for f in NVCC_FLAGS if f != "--use_fast_math"]
+        cmd = [nvcc_path(), *flags, "-I", CSRC, "-c", s, "-o", obj]
         if verbose:
             cmd.insert(1, "-Xptxas")
             cmd.insert(2, "-v")

@@ -1,0 +1,154 @@
+"""Python front-ends of csrc/seq/seq_ops.cu (ctypes -> libgllm_b200.so): the kernels of the layer-list decoder.
+
+bf16 and fp32 operands; the residual stream, norms, softmax and recurrent state are fp32 in both. No fallback: a
+missing library on a GPU box raises.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_long, c_void_p
+from typing import Optional
+
+import torch
+
+from gllm_b200.ops import lib as _lib
+from gllm_b200.ops import sm100
+from gllm_b200.ops.lib import check, stream_ptr
+
+_declared = False
+_TC_MIN = 64     # the tcgen05 GEMM takes over from this K and N on (smaller ones are latency-bound anyway)
+
+
+def _L():
+    global _declared
+    L = _lib.load()
+    if not _declared:
+        P, I, G, F = c_void_p, c_int, c_long, c_float
+        sigs = {
+            "gllm_seq_embed_scale": [P, P, P, I, I, I, F, I, P],
+            "gllm_seq_resid_norm": [P, P, G, P, P, P, P, I, I, F, I, P],
+            "gllm_seq_qk_norm_kv_write": [P, G, I, I, I, I, P, P, F, P, P, P, P, I, I, I, P],
+            "gllm_seq_window_attention": [P, P, P, P, I, P, P, I, I, F, I, I, I, I, P, P, I, I, I, P],
+            "gllm_seq_conv_silu": [P, G, I, I, I, P, P, I, P, P, P, P, P, I, P],
+            "gllm_seq_selective_scan": [P, P, P, G, P, G, P, P, P, P, P, P, P, I, I, I, I, P, I, P],
+            "gllm_seq_relu2": [P, P, G, I, P],
+            "gllm_seq_gemm_simt": [P, G, P, G, P, G, I, I, I, I, P],
+        }
+        for name, args in sigs.items():
+            fn = getattr(L, name)
+            fn.argtypes, fn.restype = args, c_int
+        _declared = True
+    return L
+
+
+def _p(t: Optional[torch.Tensor]):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _f32(t: torch.Tensor) -> int:
+    assert t.dtype in (torch.bfloat16, torch.float32), t.dtype
+    return 1 if t.dtype == torch.float32 else 0
+
+
+def gemm_simt(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    assert x.dtype == w.dtype and x.stride(1) == 1 and w.stride(1) == 1 and x.shape[1] == w.shape[1]
+    m, k = x.shape
+    n = w.shape[0]
+    out = torch.empty(m, n, dtype=x.dtype, device=x.device)
+    check(_L().gllm_seq_gemm_simt(_p(x), x.stride(0), _p(w), w.stride(0), _p(out), out.stride(0), m, n, k, _f32(x),
+                                  stream_ptr()), "seq_gemm_simt")
+    sm100._count()
+    return out
+
+
+def linear_any(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    m, k = x.shape
+    n = w.shape[0]
+    if x.dtype == torch.bfloat16 and k >= _TC_MIN and n >= _TC_MIN and k % 8 == 0 and n % 8 == 0 and \
+            x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0:
+        return sm100.linear(x, w)
+    return gemm_simt(x, w)
+
+
+def embedding_scaled(ids: torch.Tensor, table: torch.Tensor, scale: float) -> torch.Tensor:
+    t, width = ids.shape[0], table.shape[1]
+    out = torch.empty(t, width, dtype=torch.float32, device=table.device)
+    check(_L().gllm_seq_embed_scale(_p(ids), _p(table), _p(out), t, width, table.shape[0], float(scale), _f32(table),
+                                    stream_ptr()), "seq_embed_scale")
+    sm100._count()
+    return out
+
+
+def resid_norm(x, y, w_post, add, w_pre, eps, out_dtype):
+    assert x.dtype == torch.float32 and x.is_contiguous()
+    t, width = x.shape
+    out = torch.empty(t, width, dtype=out_dtype, device=x.device) if w_pre is not None else None
+    ref_t = w_pre if w_pre is not None else (w_post if w_post is not None else None)
+    is32 = 1 if (ref_t is not None and ref_t.dtype == torch.float32) or (ref_t is None and out_dtype == torch.float32) \
+        else 0
+    if y is not None:
+        assert y.stride(1) == 1 and y.dtype == w_post.dtype
+    if add is not None:
+        assert add.dtype == torch.float32 and add.is_contiguous()
+    check(_L().gllm_seq_resid_norm(_p(x), _p(y), y.stride(0) if y is not None else 0, _p(w_post), _p(add), _p(w_pre),
+                                   _p(out), t, width, float(eps), is32, stream_ptr()), "seq_resid_norm")
+    sm100._count()
+    return out
+
+
+def qk_norm_kv_write(qk, num_heads, num_kv_heads, dim, q_norm_w, k_norm_w, eps, k_cache, v_cache, slots):
+    t = qk.shape[0]
+    assert qk.stride(1) == 1 and k_cache.dtype == qk.dtype
+    q = torch.empty(t, num_heads * dim, dtype=qk.dtype, device=qk.device)
+    ps, slab = k_cache.shape[3], k_cache.shape[4]
+    check(_L().gllm_seq_qk_norm_kv_write(_p(qk), qk.stride(0), t, num_heads, num_kv_heads, dim, _p(q_norm_w),
+                                         _p(k_norm_w), float(eps), _p(q), _p(k_cache), _p(v_cache), _p(slots), ps,
+                                         slab, _f32(qk), stream_ptr()), "seq_qk_norm_kv_write")
+    sm100._count()
+    return q
+
+
+def window_attention(q, k_cache, v_cache, block_table, seq_lens, query_start_loc, positions, scale, num_q_heads,
+                     head_dim, window, sink):
+    t = q.shape[0]
+    out = torch.empty_like(q)
+    ps, slab = k_cache.shape[3], k_cache.shape[4]
+    assert q.is_contiguous() and block_table.stride(1) == 1 and positions.dim() == 1
+    check(_L().gllm_seq_window_attention(_p(q), _p(k_cache), _p(v_cache), _p(block_table), block_table.stride(0),
+                                         _p(query_start_loc), _p(positions), t, seq_lens.shape[0], float(scale),
+                                         num_q_heads, k_cache.shape[1], head_dim, int(window or 0), _p(sink), _p(out),
+                                         ps, slab, _f32(q), stream_ptr()), "seq_window_attention")
+    sm100._count()
+    return out
+
+
+def causal_conv_silu(xz, channels, w, b, conv_state, rec_slots, seq_lens, query_start_loc):
+    t = xz.shape[0]
+    assert xz.stride(1) == 1 and w.dtype == torch.float32 and b.dtype == torch.float32
+    out = torch.empty(t, channels, dtype=xz.dtype, device=xz.device)
+    check(_L().gllm_seq_conv_silu(_p(xz), xz.stride(0), t, seq_lens.shape[0], channels, _p(w), _p(b), w.shape[1],
+                                  _p(conv_state), _p(rec_slots), _p(seq_lens), _p(query_start_loc), _p(out), _f32(xz),
+                                  stream_ptr()), "seq_conv_silu")
+    sm100._count(2 if conv_state is not None else 1)
+    return out
+
+
+def selective_scan(xc, dt_raw, proj, xz, a, d_skip, dt_bias, ssm_state, rec_slots, seq_lens, query_start_loc,
+                   channels, nstate, dt_rank):
+    assert xc.is_contiguous() and dt_raw.is_contiguous() and proj.stride(1) == 1 and xz.stride(1) == 1
+    assert a.dtype == torch.float32 and a.is_contiguous()
+    out = torch.empty_like(xc)
+    check(_L().gllm_seq_selective_scan(_p(xc), _p(dt_raw), _p(proj), proj.stride(0), _p(xz), xz.stride(0), _p(a),
+                                       _p(d_skip), _p(dt_bias), _p(ssm_state), _p(rec_slots), _p(seq_lens),
+                                       _p(query_start_loc), seq_lens.shape[0], channels, nstate, dt_rank, _p(out),
+                                       _f32(xc), stream_ptr()), "seq_selective_scan")
+    sm100._count()
+    return out
+
+
+def relu2(x):
+    x = x.contiguous()
+    out = torch.empty_like(x)
+    check(_L().gllm_seq_relu2(_p(x), _p(out), x.numel(), _f32(x), stream_ptr()), "seq_relu2")
+    sm100._count()
+    return out
