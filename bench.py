@@ -57,6 +57,9 @@ def parse():
     ap.add_argument("--layers", type=int, default=0, help="override num_hidden_layers (0 = the model's own); a "
                     "reduced depth is reported in `config.model` and is NOT the named model")
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--design", default=None, choices=["saritar"],
+                    help="side benchmark: prefill / decode throughput and kernel rooflines of that design beside "
+                         "the closest existing decoder at equal size (benchmarks/design_bench.py); 1 GPU")
     ap.add_argument("--async-schedule", action=argparse.BooleanOptionalAction, default=True,
                     help="lookahead decode scheduling (engine default; --no-async-schedule for the synchronous loop)")
     ap.add_argument("--disable-cuda-graph", action="store_true", help="debugging: every step runs eagerly")
@@ -206,6 +209,11 @@ def main():
     args = parse()
     if args.impl == "reference":
         return reference_arm(args)
+    if args.design:
+        sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+        from benchmarks import design_bench
+        design_bench.run(args)
+        return 0
     import torch
     import torch.distributed as dist
     from gllm_b200 import LLM

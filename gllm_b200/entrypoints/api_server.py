@@ -293,6 +293,10 @@ def make_parser() -> argparse.ArgumentParser:
     p.add_argument("--mm-processor-min-pixels", type=int, default=None)
     p.add_argument("--mm-processor-max-pixels", type=int, default=None)
     p.add_argument("--tp-mode", type=str, default="fused", choices=["fused", "nccl"])
+    p.add_argument("--dtype", type=str, default=None, choices=["bfloat16", "float32"],
+                   help="override the checkpoint's compute dtype (float32: layer-list decoders only)")
+    p.add_argument("--num-state-slots", type=int, default=None,
+                   help="recurrent-state slots = most sequences running at once (models with per-sequence state)")
     return p
 
 
@@ -308,7 +312,8 @@ def engine_kwargs(args) -> dict:
                 schedule_method=args.schedule_method, disable_cuda_graph=args.disable_cuda_graph,
                 max_cuda_graph_bs=args.max_cuda_graph_bs, model_max_length=args.model_max_length,
                 mm_processor_min_pixels=args.mm_processor_min_pixels,
-                mm_processor_max_pixels=args.mm_processor_max_pixels, tp_mode=args.tp_mode)
+                mm_processor_max_pixels=args.mm_processor_max_pixels, tp_mode=args.tp_mode,
+                dtype=args.dtype, num_state_slots=args.num_state_slots)
 
 
 async def run_server(app, host: str, port: int):

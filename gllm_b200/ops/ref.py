@@ -553,7 +553,7 @@ def causal_conv_silu(xz: torch.Tensor, channels: int, w: torch.Tensor, b: torch.
         x = xz[q0:q1, :channels].float()
         hist = torch.zeros(taps - 1, channels, dtype=torch.float32, device=xz.device)
         if conv_state is not None and sl[s] - n > 0:
-            hist = conv_state[int(rec_slots[s])].float()
+            hist = conv_state[int(rec_slots[s])][: taps - 1].float()
         xp = torch.cat([hist, x], 0)
         acc = b.float().expand(n, channels).clone()
         for j in range(taps):
