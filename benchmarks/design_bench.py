@@ -34,7 +34,7 @@ def _qwen3_cfg(width, layers, heads, kv, dim, inter, vocab):
 def _throughput(cfg, vocab, warmup, steps):
     from gllm_b200.engine.llm_engine import LLM
     llm = LLM(cfg, load_format="dummy", maxp=8192, maxd=256, max_cuda_graph_bs=64, model_max_length=4096,
-              enable_prefix_caching=False, log_stats=False, launch_mode="inproc", gpu_memory_util=0.5,
+              enable_prefix_caching=False, log_stats=False, launch_mode="inproc", num_gpu_pages=4096,
               num_state_slots=64)
     params = sum(p.numel() for p in llm.worker.runner.model.parameters())
     g = torch.Generator().manual_seed(0)
@@ -57,7 +57,10 @@ def _throughput(cfg, vocab, warmup, steps):
         tok = n * plen if name == "prefill" else n * olen
         res[name + "_tok_s"] = round(tok / best, 1)
     llm.worker.runner.close()
+    llm.worker.runner.kv_cache = llm.worker.runner.model = None
     del llm
+    import gc
+    gc.collect()
     torch.cuda.empty_cache()
     return res
 
@@ -151,6 +154,7 @@ def run(args):
         with open(p) as f:
             peaks = json.load(f)
     vocab = 32000
+    kernels = _kernels(peaks)
     sizes = []
     for width, pairs, heads, kv in ((1024, 4, 8, 2), (2048, 4, 16, 4), (4096, 2, 32, 8)):
         s_cfg = _saritar_cfg(width, pairs, heads, kv, 128, 1024, 4 * width, vocab)
@@ -160,6 +164,6 @@ def run(args):
                       "qwen3": _throughput(q_cfg, vocab, args.warmup, args.steps)})
     line = {"design": "saritar", "dtype": "bf16", "data": "synthetic", "warmup": args.warmup, "steps": args.steps,
             "timing": "wall clock around LLM.generate with synchronize (sizes); CUDA events, L2 flushed (kernels)",
-            "peaks": peaks, "sizes": sizes, "kernels": _kernels(peaks)}
+            "peaks": peaks, "sizes": sizes, "kernels": kernels}
     print(json.dumps(line))
     return line
