@@ -135,7 +135,9 @@ def _kernels(peaks):
         q = torch.randn(Tt, H * D, device=dev).to(bf)
         sink = torch.zeros(H, device=dev)
         keys = sum(min(p + 1, win) for ql in qlens for p in range(ctx, ctx + ql))
-        ms = _time(lambda: S.window_attention(q, kc, vc, bt, sl, qsl, pos, D ** -0.5, H, D, win, sink), iters=3)
+        nd = B if qlens[0] == 1 else 0
+        ms = _time(lambda: S.window_attention(q, kc, vc, bt, sl, qsl, pos, D ** -0.5, H, D, win, sink,
+                                              num_decode_seqs=nd, max_q_len=max(qlens)), iters=5)
         r = {"kernel": "window_attention " + label, "ms": round(ms, 4),
              "tflops": round(4.0 * keys * H * D / ms / 1e9, 2)}
         ms2 = _time(lambda: sm100.paged_attention(q, kc, vc, bt, sl, qsl, D ** -0.5, H, D,

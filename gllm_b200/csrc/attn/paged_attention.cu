@@ -35,6 +35,10 @@ struct AttnParams {
   // decode with num_splits > 1: arrival counter per (sequence, head group); the LAST split CTA to finish merges
   // the partial results itself (no separate merge launch). Zero at rest, re-armed by the merging CTA.
   uint32_t* split_cnt;
+  // sliding window: a query at position i sees keys j with i - j < window (0 = the whole past); sink: one extra
+  // logit per query head in the softmax denominator that carries no value (null = none; decode: num_splits == 1)
+  int window;
+  const float* sink;
 };
 
 template <int D>
@@ -98,8 +102,10 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_cons
   const int split = blockIdx.z;
   const int seq_len = p.seq_lens[seq];
   const int n_tiles = (seq_len + kTileN - 1) / kTileN;
-  const int tps = (n_tiles + p.num_splits - 1) / p.num_splits;
-  const int tile_begin = min(split * tps, n_tiles);
+  const int win_lo = p.window > 0 ? max(0, seq_len - p.window) : 0;   // first visible key
+  const int tile_lo = win_lo / kTileN;
+  const int tps = (n_tiles - tile_lo + p.num_splits - 1) / p.num_splits;
+  const int tile_begin = min(tile_lo + split * tps, n_tiles);
   const int tile_end = min(tile_begin + tps, n_tiles);
   const int page_bytes = p.page_size * D * 2;
 
@@ -175,7 +181,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_cons
       for (int e = 0; e < 4; ++e) {
         const int col = abs0 + nt * 8 + (e & 1);
         float v = sc[nt][e] * p.scale_log2;
-        if (col >= seq_len) v = -INFINITY;
+        if (col >= seq_len || col < win_lo) v = -INFINITY;
         sc[nt][e] = v;
         mx[e >> 1] = fmaxf(mx[e >> 1], v);
       }
@@ -262,8 +268,10 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_cons
       wgt[w] = (mw[w] == -INFINITY) ? 0.f : exp2f(mw[w] - m_all);
       l_all += wgt[w] * red_l[w * 16 + row];
     }
-    const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
     const int head = hbase + row;
+    if (p.sink != nullptr && p.num_splits == 1 && m_all > -INFINITY)
+      l_all += exp2f(p.sink[head] * 1.4426950408889634f - m_all);
+    const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
     for (int c = (tid & 7) * 4; c < D; c += 32) {
       float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
@@ -378,6 +386,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
   const int last_tok = min(tok_base + toks_per_tile, q_len) - 1;
   const int kv_end = ctx_len + last_tok + 1;  // causal horizon of this tile
   const int n_tiles = (kv_end + kTileN - 1) / kTileN;
+  const int tile_lo = p.window > 0 ? max(0, ctx_len + tok_base - p.window + 1) / kTileN : 0;   // first query's window
   const int page_bytes = p.page_size * D * 2;
 
   if (threadIdx.x == 0) {
@@ -392,7 +401,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
   if (warp == kMathWarps) {
     if (lane == 0) {
       kv_producer<D>(&tmap_k, &tmap_v, smem, full_bar, empty_bar, p.block_table + (size_t)seq * p.max_blocks, kvh,
-                     p.Hkv, p.page_size, seq_len, 0, n_tiles);
+                     p.Hkv, p.page_size, seq_len, tile_lo, n_tiles);
     }
     return;
   }
@@ -426,9 +435,10 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
   float l_run[2] = {0.f, 0.f};
   const int lim[2] = {ctx_len + r_tok[0], ctx_len + r_tok[1]};  // last visible key per row
 
-  for (int tile = 0; tile < n_tiles; ++tile) {
-    const int s = tile % SM::kStages;
-    const uint32_t ph = (tile / SM::kStages) & 1;
+  uint32_t it = 0;
+  for (int tile = tile_lo; tile < n_tiles; ++tile, ++it) {
+    const int s = it % SM::kStages;
+    const uint32_t ph = (it / SM::kStages) & 1;
     mbar_wait(&full_bar[s], ph);
     const uint32_t sk = smem_u32(smem + s * SM::kStageBytes);
     const uint32_t sv = sk + SM::kTileBytes;
@@ -456,7 +466,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
       for (int e = 0; e < 4; ++e) {
         const int col = abs0 + nt * 8 + (e & 1);
         float v = sc[nt][e] * p.scale_log2;
-        if (col > lim[e >> 1]) v = -INFINITY;
+        if (col > lim[e >> 1] || (p.window > 0 && col <= lim[e >> 1] - p.window)) v = -INFINITY;
         sc[nt][e] = v;
         mx[e >> 1] = fmaxf(mx[e >> 1], v);
       }
@@ -516,7 +526,9 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
     if (!r_ok[r]) continue;
-    const float inv = l_run[r] > 0.f ? 1.f / l_run[r] : 0.f;
+    float den = l_run[r];
+    if (p.sink != nullptr && m_run[r] > -INFINITY) den += exp2f(p.sink[r_head[r]] * 1.4426950408889634f - m_run[r]);
+    const float inv = den > 0.f ? 1.f / den : 0.f;
     __nv_bfloat16* op = p.out + ((size_t)(q_begin + r_tok[r]) * p.Hq + r_head[r]) * D + 2 * t;
 #pragma unroll
     for (int nd = 0; nd < D / 8; ++nd) {
@@ -579,10 +591,15 @@ using namespace b200;
 
 // Decode: one query token per sequence; q row i belongs to sequence seq_offset + i... (q is indexed
 // by the absolute sequence index, as are block_table / seq_lens).
-GLLM_EXPORT int gllm_attn_decode(const void* q, int64_t q_ts, void* out, const void* k_cache, const void* v_cache,
-                                 int64_t num_pages, const void* block_table, const void* seq_lens, void* part_o,
-                                 void* part_lse, int num_seqs, int seq_offset, int max_blocks, int Hq, int Hkv,
-                                 int D, int page_size, int num_splits, float scale, void* split_cnt, void* stream) {
+static int attn_decode_impl(const void* q, int64_t q_ts, void* out, const void* k_cache, const void* v_cache,
+                            int64_t num_pages, const void* block_table, const void* seq_lens, void* part_o,
+                            void* part_lse, int num_seqs, int seq_offset, int max_blocks, int Hq, int Hkv,
+                            int D, int page_size, int num_splits, float scale, void* split_cnt, void* stream,
+                            int window, const void* sink) {
+  if (sink != nullptr && num_splits > 1) {
+    fprintf(stderr, "[gllm_b200] attn_decode: a softmax sink needs num_splits == 1\n");
+    return 1;
+  }
   if (num_seqs <= 0) return 0;
   if (page_size < 8 || kTileN % page_size != 0 || Hq % Hkv != 0) {
     fprintf(stderr, "[gllm_b200] attn_decode: unsupported page_size=%d / heads\n", page_size);
@@ -605,6 +622,7 @@ GLLM_EXPORT int gllm_attn_decode(const void* q, int64_t q_ts, void* out, const v
   p.seq_offset = seq_offset;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.split_cnt = reinterpret_cast<uint32_t*>(split_cnt);
+  p.window = window; p.sink = reinterpret_cast<const float*>(sink);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   int rc;
   switch (D) {
@@ -626,11 +644,32 @@ GLLM_EXPORT int gllm_attn_decode(const void* q, int64_t q_ts, void* out, const v
   return 0;
 }
 
+GLLM_EXPORT int gllm_attn_decode(const void* q, int64_t q_ts, void* out, const void* k_cache, const void* v_cache,
+                                 int64_t num_pages, const void* block_table, const void* seq_lens, void* part_o,
+                                 void* part_lse, int num_seqs, int seq_offset, int max_blocks, int Hq, int Hkv,
+                                 int D, int page_size, int num_splits, float scale, void* split_cnt, void* stream) {
+  return attn_decode_impl(q, q_ts, out, k_cache, v_cache, num_pages, block_table, seq_lens, part_o, part_lse,
+                          num_seqs, seq_offset, max_blocks, Hq, Hkv, D, page_size, num_splits, scale, split_cnt,
+                          stream, 0, nullptr);
+}
+
+// the same with a sliding window (0 = none) and a per-head softmax sink (null = none)
+GLLM_EXPORT int gllm_attn_decode_win(const void* q, int64_t q_ts, void* out, const void* k_cache,
+                                     const void* v_cache, int64_t num_pages, const void* block_table,
+                                     const void* seq_lens, int num_seqs, int seq_offset, int max_blocks, int Hq,
+                                     int Hkv, int D, int page_size, float scale, int window, const void* sink,
+                                     void* stream) {
+  return attn_decode_impl(q, q_ts, out, k_cache, v_cache, num_pages, block_table, seq_lens, nullptr, nullptr,
+                          num_seqs, seq_offset, max_blocks, Hq, Hkv, D, page_size, 1, scale, nullptr, stream, window,
+                          sink);
+}
+
 // Prefill / mixed: sequences [seq_offset, seq_offset + num_seqs) with query ranges q_start[seq]..q_start[seq+1]
-GLLM_EXPORT int gllm_attn_prefill(const void* q, int64_t q_ts, void* out, const void* k_cache, const void* v_cache,
-                                  int64_t num_pages, const void* block_table, const void* seq_lens,
-                                  const void* q_start, int num_seqs, int seq_offset, int max_q_len, int max_blocks,
-                                  int Hq, int Hkv, int D, int page_size, float scale, void* stream) {
+static int attn_prefill_impl(const void* q, int64_t q_ts, void* out, const void* k_cache, const void* v_cache,
+                             int64_t num_pages, const void* block_table, const void* seq_lens,
+                             const void* q_start, int num_seqs, int seq_offset, int max_q_len, int max_blocks,
+                             int Hq, int Hkv, int D, int page_size, float scale, void* stream, int window,
+                             const void* sink) {
   if (num_seqs <= 0 || max_q_len <= 0) return 0;
   if (page_size < 8 || kTileN % page_size != 0 || Hq % Hkv != 0) {
     fprintf(stderr, "[gllm_b200] attn_prefill: unsupported page_size=%d / heads\n", page_size);
@@ -650,6 +689,7 @@ GLLM_EXPORT int gllm_attn_prefill(const void* q, int64_t q_ts, void* out, const 
   p.GP = largest_divisor_leq(p.G, 64, 64);
   p.page_size = page_size; p.num_splits = 1; p.seq_offset = seq_offset;
   p.scale_log2 = scale * 1.4426950408889634f;
+  p.split_cnt = nullptr; p.window = window; p.sink = reinterpret_cast<const float*>(sink);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   switch (D) {
     case 64: return launch_prefill<64>(tk, tv, p, num_seqs, max_q_len, st);
@@ -659,4 +699,21 @@ GLLM_EXPORT int gllm_attn_prefill(const void* q, int64_t q_ts, void* out, const 
       fprintf(stderr, "[gllm_b200] attn_prefill: unsupported head_dim %d\n", D);
       return 1;
   }
+}
+
+GLLM_EXPORT int gllm_attn_prefill(const void* q, int64_t q_ts, void* out, const void* k_cache, const void* v_cache,
+                                  int64_t num_pages, const void* block_table, const void* seq_lens,
+                                  const void* q_start, int num_seqs, int seq_offset, int max_q_len, int max_blocks,
+                                  int Hq, int Hkv, int D, int page_size, float scale, void* stream) {
+  return attn_prefill_impl(q, q_ts, out, k_cache, v_cache, num_pages, block_table, seq_lens, q_start, num_seqs,
+                           seq_offset, max_q_len, max_blocks, Hq, Hkv, D, page_size, scale, stream, 0, nullptr);
+}
+
+GLLM_EXPORT int gllm_attn_prefill_win(const void* q, int64_t q_ts, void* out, const void* k_cache,
+                                      const void* v_cache, int64_t num_pages, const void* block_table,
+                                      const void* seq_lens, const void* q_start, int num_seqs, int seq_offset,
+                                      int max_q_len, int max_blocks, int Hq, int Hkv, int D, int page_size,
+                                      float scale, int window, const void* sink, void* stream) {
+  return attn_prefill_impl(q, q_ts, out, k_cache, v_cache, num_pages, block_table, seq_lens, q_start, num_seqs,
+                           seq_offset, max_q_len, max_blocks, Hq, Hkv, D, page_size, scale, stream, window, sink);
 }

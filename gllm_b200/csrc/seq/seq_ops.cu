@@ -228,6 +228,39 @@ __global__ void conv_silu_kernel(const T* __restrict__ xz, long ldxz, int C, con
   out[(size_t)t * C + c] = from_f<T>(acc / (1.0f + expf(-acc)));
 }
 
+// bf16, C % 8 == 0: eight channels per thread, 16-byte loads and stores
+__global__ void conv_silu_vec8_kernel(const __nv_bfloat16* __restrict__ xz, long ldxz, int C,
+                                      const float* __restrict__ w, const float* __restrict__ b, int taps,
+                                      const __nv_bfloat16* __restrict__ state, const int* __restrict__ rec_slots,
+                                      const int* __restrict__ seq_lens, const int* __restrict__ qsl, int nseq,
+                                      __nv_bfloat16* __restrict__ out) {
+  const int t = blockIdx.x;
+  const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+  if (c >= C) return;
+  const int s = find_seq(qsl, nseq, t);
+  const int q0 = qsl[s], n = qsl[s + 1] - q0;
+  const bool carried = state != nullptr && (seq_lens[s] - n) > 0;
+  const __nv_bfloat16* st = carried ? state + (size_t)rec_slots[s] * (taps > 1 ? taps - 1 : 1) * C : nullptr;
+  const int li = t - q0;
+  float acc[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) acc[e] = b[c + e];
+  for (int j = 0; j < taps; ++j) {
+    const int src = li - (taps - 1) + j;
+    uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+    if (src >= 0) raw = *reinterpret_cast<const uint4*>(xz + (size_t)(q0 + src) * ldxz + c);
+    else if (carried) raw = *reinterpret_cast<const uint4*>(st + (size_t)(taps - 1 + src) * C + c);
+    const __nv_bfloat16* v = reinterpret_cast<const __nv_bfloat16*>(&raw);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = fmaf(w[(size_t)(c + e) * taps + j], __bfloat162float(v[e]), acc[e]);
+  }
+  uint4 o;
+  __nv_bfloat16* ov = reinterpret_cast<__nv_bfloat16*>(&o);
+#pragma unroll
+  for (int e = 0; e < 8; ++e) ov[e] = __float2bfloat16_rn(acc[e] / (1.0f + expf(-acc[e])));
+  *reinterpret_cast<uint4*>(out + (size_t)t * C + c) = o;
+}
+
 // after the convolution: state <- the last taps - 1 inputs of the sequence (shifting in what the chunk brought)
 template <typename T>
 __global__ void conv_state_update_kernel(const T* __restrict__ xz, long ldxz, int C, int taps, T* __restrict__ state,
@@ -249,48 +282,81 @@ __global__ void conv_state_update_kernel(const T* __restrict__ xz, long ldxz, in
   }
 }
 
-// Mamba-1 recurrence: one thread per channel holds its N states in registers and walks the sequence's tokens.
-template <typename T, int NMAX>
+// Mamba-1 recurrence: one thread per channel holds its N states in registers and walks the sequence's tokens in
+// chunks of TCH: the chunk's B and C rows (shared by all channels) are staged in shared memory by the whole block and
+// the thread's own dt / x / z values are fetched up front, so the serial loop runs out of registers and smem.
+template <typename T, int NMAX, int PARTS>
 __global__ void __launch_bounds__(64) selective_scan_kernel(
     const T* __restrict__ xc, const T* __restrict__ dt_raw, const T* __restrict__ proj, long ldp,
     const T* __restrict__ xz, long ldxz, const float* __restrict__ A, const float* __restrict__ Dskip,
     const float* __restrict__ dt_bias, float* __restrict__ state, const int* __restrict__ rec_slots,
     const int* __restrict__ seq_lens, const int* __restrict__ qsl, int C, int N, int R, T* __restrict__ out) {
+  constexpr int TCH = 8;
+  __shared__ float sBC[TCH][2 * NMAX];
   const int s = blockIdx.x;
-  const int c = blockIdx.y * 64 + threadIdx.x;
+  // PARTS threads share a channel (state n = part + PARTS * j): more warps in flight when few sequences are long
+  constexpr int NS = NMAX / PARTS;
+  const int c0 = (blockIdx.y * 64 + threadIdx.x) / PARTS, part = threadIdx.x % PARTS;
   const int q0 = qsl[s], q1 = qsl[s + 1];
-  if (c >= C || q1 <= q0) return;
+  if (q1 <= q0) return;                       // uniform over the block
+  const bool active = c0 < C;
+  const int c = active ? c0 : C - 1;          // idle threads mirror the last channel (loads only)
   const bool carried = state != nullptr && (seq_lens[s] - (q1 - q0)) > 0;
   float* st = state != nullptr ? state + (size_t)rec_slots[s] * N * C : nullptr;
-  float S[NMAX], a[NMAX];
+  float S[NS], a[NS];
 #pragma unroll
-  for (int n = 0; n < NMAX; ++n) {
-    a[n] = n < N ? A[(size_t)c * N + n] : 0.f;
-    S[n] = (carried && n < N) ? st[(size_t)n * C + c] : 0.f;
+  for (int j = 0; j < NS; ++j) {
+    const int n = part + PARTS * j;
+    a[j] = n < N ? A[(size_t)c * N + n] : 0.f;
+    S[j] = (carried && n < N) ? st[(size_t)n * C + c] : 0.f;
   }
   const float dsk = Dskip[c], bias = dt_bias[c];
-  for (int t = q0; t < q1; ++t) {
-    const float v = to_f(dt_raw[(size_t)t * C + c]) + bias;
-    const float dt = v > 20.0f ? v : log1pf(expf(v));
-    const float x = to_f(xc[(size_t)t * C + c]);
-    const float z = to_f(xz[(size_t)t * ldxz + C + c]);
-    const T* bp = proj + (size_t)t * ldp + R;
-    const float dx = dt * x;
-    float y = 0.f;
+  for (int t0 = q0; t0 < q1; t0 += TCH) {
+    const int nt = min(TCH, q1 - t0);
+    __syncthreads();                          // the previous chunk's rows are consumed
+    for (int idx = threadIdx.x; idx < nt * 2 * N; idx += 64) {
+      const int k = idx / (2 * N), n = idx - k * 2 * N;
+      sBC[k][n] = to_f(proj[(size_t)(t0 + k) * ldp + R + n]);
+    }
+    float dtv[TCH], xv[TCH], zv[TCH];
 #pragma unroll
-    for (int n = 0; n < NMAX; ++n) {
-      if (n < N) {
-        S[n] = expf(dt * a[n]) * S[n] + dx * to_f(bp[n]);
-        y = fmaf(S[n], to_f(bp[N + n]), y);
+    for (int k = 0; k < TCH; ++k) {
+      if (k < nt) {
+        dtv[k] = to_f(dt_raw[(size_t)(t0 + k) * C + c]);
+        xv[k] = to_f(xc[(size_t)(t0 + k) * C + c]);
+        zv[k] = to_f(xz[(size_t)(t0 + k) * ldxz + C + c]);
       }
     }
-    y = fmaf(dsk, x, y);
-    out[(size_t)t * C + c] = from_f<T>(y * (z / (1.0f + expf(-z))));
-  }
-  if (st != nullptr) {
+    __syncthreads();
 #pragma unroll
-    for (int n = 0; n < NMAX; ++n)
-      if (n < N) st[(size_t)n * C + c] = S[n];
+    for (int k = 0; k < TCH; ++k) {
+      if (k < nt) {
+        const float v = dtv[k] + bias;
+        const float dt = v > 20.0f ? v : log1pf(expf(v));
+        const float x = xv[k], z = zv[k];
+        const float dx = dt * x;
+        float y = 0.f;
+#pragma unroll
+        for (int j = 0; j < NS; ++j) {
+          const int n = part + PARTS * j;
+          if (n < N) {
+            S[j] = expf(dt * a[j]) * S[j] + dx * sBC[k][n];
+            y = fmaf(S[j], sBC[k][N + n], y);
+          }
+        }
+#pragma unroll
+        for (int o = 1; o < PARTS; o <<= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
+        y = fmaf(dsk, x, y);
+        if (active && part == 0) out[(size_t)(t0 + k) * C + c] = from_f<T>(y * (z / (1.0f + expf(-z))));
+      }
+    }
+  }
+  if (st != nullptr && active) {
+#pragma unroll
+    for (int j = 0; j < NS; ++j) {
+      const int n = part + PARTS * j;
+      if (n < N) st[(size_t)n * C + c] = S[j];
+    }
   }
 }
 
@@ -339,12 +405,12 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const T* __restrict__ A,
     }
 }
 
-template <typename T>
+template <typename T, int PARTS>
 int scan_dispatch(int nmax, dim3 grid, cudaStream_t st, const void* xc, const void* dt_raw, const void* proj, long ldp,
                   const void* xz, long ldxz, const float* A, const float* Dskip, const float* dt_bias, float* state,
                   const int* rec_slots, const int* seq_lens, const int* qsl, int C, int N, int R, void* out) {
 #define GLLM_SCAN(NM)                                                                                             \
-  selective_scan_kernel<T, NM><<<grid, 64, 0, st>>>((const T*)xc, (const T*)dt_raw, (const T*)proj, ldp,          \
+  selective_scan_kernel<T, NM, PARTS><<<grid, 64, 0, st>>>((const T*)xc, (const T*)dt_raw, (const T*)proj, ldp,          \
                                                     (const T*)xz, ldxz, A, Dskip, dt_bias, state, rec_slots,      \
                                                     seq_lens, qsl, C, N, R, (T*)out)
   if (nmax <= 8) GLLM_SCAN(8);
@@ -461,9 +527,16 @@ GLLM_EXPORT int gllm_seq_conv_silu(const void* xz, long ldxz, int ntok, int nseq
                                                              (const int*)rec_slots, (const int*)seq_lens,
                                                              (const int*)qsl);
   } else {
-    conv_silu_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>(
-        (const __nv_bfloat16*)xz, ldxz, C, (const float*)w, (const float*)b, taps, (const __nv_bfloat16*)state,
-        (const int*)rec_slots, (const int*)seq_lens, (const int*)qsl, nseq, (__nv_bfloat16*)out);
+    const bool vec = C % 8 == 0 && ldxz % 8 == 0 && ((uintptr_t)xz % 16) == 0 && ((uintptr_t)out % 16) == 0 &&
+                     (state == nullptr || (uintptr_t)state % 16 == 0);
+    if (vec)
+      conv_silu_vec8_kernel<<<dim3(ntok, (C / 8 + 127) / 128), 128, 0, st>>>(
+          (const __nv_bfloat16*)xz, ldxz, C, (const float*)w, (const float*)b, taps, (const __nv_bfloat16*)state,
+          (const int*)rec_slots, (const int*)seq_lens, (const int*)qsl, nseq, (__nv_bfloat16*)out);
+    else
+      conv_silu_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>(
+          (const __nv_bfloat16*)xz, ldxz, C, (const float*)w, (const float*)b, taps, (const __nv_bfloat16*)state,
+          (const int*)rec_slots, (const int*)seq_lens, (const int*)qsl, nseq, (__nv_bfloat16*)out);
     if (state != nullptr && taps > 1)
       conv_state_update_kernel<__nv_bfloat16><<<sgrid, 128, 0, st>>>(
           (const __nv_bfloat16*)xz, ldxz, C, taps, (__nv_bfloat16*)state, (const int*)rec_slots, (const int*)seq_lens,
@@ -476,17 +549,31 @@ GLLM_EXPORT int gllm_seq_conv_silu(const void* xz, long ldxz, int ntok, int nseq
 GLLM_EXPORT int gllm_seq_selective_scan(const void* xc, const void* dt_raw, const void* proj, long ldp, const void* xz,
                                         long ldxz, const void* A, const void* Dskip, const void* dt_bias, void* state,
                                         const void* rec_slots, const void* seq_lens, const void* qsl, int nseq, int C,
-                                        int N, int R, void* out, int is_f32, void* stream) {
+                                        int N, int R, void* out, int is_f32, int parts, void* stream) {
   if (nseq <= 0) return 0;
   cudaStream_t st = (cudaStream_t)stream;
-  dim3 grid(nseq, (C + 63) / 64);
   int rc;
+  if (parts == 4 && N >= 8) {       // few long sequences: 4 threads per channel
+    dim3 grid4(nseq, (C + 15) / 16);
+    if (is_f32)
+      rc = scan_dispatch<float, 4>(N, grid4, st, xc, dt_raw, proj, ldp, xz, ldxz, (const float*)A,
+                                   (const float*)Dskip, (const float*)dt_bias, (float*)state, (const int*)rec_slots,
+                                   (const int*)seq_lens, (const int*)qsl, C, N, R, out);
+    else
+      rc = scan_dispatch<__nv_bfloat16, 4>(N, grid4, st, xc, dt_raw, proj, ldp, xz, ldxz, (const float*)A,
+                                           (const float*)Dskip, (const float*)dt_bias, (float*)state,
+                                           (const int*)rec_slots, (const int*)seq_lens, (const int*)qsl, C, N, R, out);
+    if (rc) return rc;
+    CUDA_CHECK_RET(cudaGetLastError());
+    return 0;
+  }
+  dim3 grid(nseq, (C + 63) / 64);
   if (is_f32)
-    rc = scan_dispatch<float>(N, grid, st, xc, dt_raw, proj, ldp, xz, ldxz, (const float*)A, (const float*)Dskip,
+    rc = scan_dispatch<float, 1>(N, grid, st, xc, dt_raw, proj, ldp, xz, ldxz, (const float*)A, (const float*)Dskip,
                               (const float*)dt_bias, (float*)state, (const int*)rec_slots, (const int*)seq_lens,
                               (const int*)qsl, C, N, R, out);
   else
-    rc = scan_dispatch<__nv_bfloat16>(N, grid, st, xc, dt_raw, proj, ldp, xz, ldxz, (const float*)A,
+    rc = scan_dispatch<__nv_bfloat16, 1>(N, grid, st, xc, dt_raw, proj, ldp, xz, ldxz, (const float*)A,
                                       (const float*)Dskip, (const float*)dt_bias, (float*)state,
                                       (const int*)rec_slots, (const int*)seq_lens, (const int*)qsl, C, N, R, out);
   if (rc) return rc;

@@ -141,7 +141,9 @@ def qk_norm_kv_write(qk, num_heads, num_kv_heads, dim, q_norm_w, k_norm_w, eps, 
 def window_attention(q, k_cache, v_cache, inp, scale, num_q_heads, head_dim, window, sink):
     if q.is_cuda:
         return _seq().window_attention(q, k_cache, v_cache, inp.block_table, inp.seq_lens, inp.query_start_loc,
-                                       inp.positions, scale, num_q_heads, head_dim, window, sink)
+                                       inp.positions, scale, num_q_heads, head_dim, window, sink,
+                                       num_decode_seqs=inp.padded_tokens or inp.num_decode_seqs,
+                                       max_q_len=inp.max_q_len)
     return ref.window_attention(q, k_cache, v_cache, inp.block_table, inp.seq_lens, inp.query_start_loc, scale,
                                 num_q_heads, head_dim, window, sink)
 

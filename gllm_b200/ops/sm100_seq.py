@@ -30,9 +30,11 @@ def _L():
             "gllm_seq_qk_norm_kv_write": [P, G, I, I, I, I, P, P, F, P, P, P, P, I, I, I, P],
             "gllm_seq_window_attention": [P, P, P, P, I, P, P, I, I, F, I, I, I, I, P, P, I, I, I, P],
             "gllm_seq_conv_silu": [P, G, I, I, I, P, P, I, P, P, P, P, P, I, P],
-            "gllm_seq_selective_scan": [P, P, P, G, P, G, P, P, P, P, P, P, P, I, I, I, I, P, I, P],
+            "gllm_seq_selective_scan": [P, P, P, G, P, G, P, P, P, P, P, P, P, I, I, I, I, P, I, I, P],
             "gllm_seq_relu2": [P, P, G, I, P],
             "gllm_seq_gemm_simt": [P, G, P, G, P, G, I, I, I, I, P],
+            "gllm_attn_decode_win": [P, G, P, P, P, G, P, P, I, I, I, I, I, I, I, F, I, P, P],
+            "gllm_attn_prefill_win": [P, G, P, P, P, G, P, P, P, I, I, I, I, I, I, I, I, F, I, P, P],
         }
         for name, args in sigs.items():
             fn = getattr(L, name)
@@ -109,11 +111,35 @@ def qk_norm_kv_write(qk, num_heads, num_kv_heads, dim, q_norm_w, k_norm_w, eps, 
 
 
 def window_attention(q, k_cache, v_cache, block_table, seq_lens, query_start_loc, positions, scale, num_q_heads,
-                     head_dim, window, sink):
+                     head_dim, window, sink, num_decode_seqs: int = 0, max_q_len: Optional[int] = None,
+                     simt: bool = False):
+    """Sliding-window (None / 0 = full causal) paged attention with an optional per-head softmax sink. bf16 with
+    head_dim 64 / 128 / 256 and pages of 8..64 tokens runs on the tensor-core paged-attention kernels
+    (csrc/attn/paged_attention.cu: the first `num_decode_seqs` sequences, one token each, on the decode kernel, the
+    rest on the prefill kernel); everything else (fp32, other head sizes or page sizes) on the plain kernel."""
     t = q.shape[0]
     out = torch.empty_like(q)
     ps, slab = k_cache.shape[3], k_cache.shape[4]
     assert q.is_contiguous() and block_table.stride(1) == 1 and positions.dim() == 1
+    nseq = seq_lens.shape[0]
+    if not simt and q.dtype == torch.bfloat16 and head_dim in (64, 128, 256) and slab == 64 and ps >= 8 and \
+            64 % ps == 0 and max_q_len is not None:
+        L, st = _L(), stream_ptr()
+        pages, hkv = k_cache.shape[0], k_cache.shape[1]
+        if num_decode_seqs > 0:
+            check(L.gllm_attn_decode_win(_p(q), q.stride(0), _p(out), _p(k_cache), _p(v_cache), pages, _p(block_table),
+                                         _p(seq_lens), num_decode_seqs, 0, block_table.stride(0), num_q_heads, hkv,
+                                         head_dim, ps, float(scale), int(window or 0), _p(sink), st),
+                  "attn_decode_win")
+            sm100._count()
+        if nseq > num_decode_seqs:
+            check(L.gllm_attn_prefill_win(_p(q), q.stride(0), _p(out), _p(k_cache), _p(v_cache), pages,
+                                          _p(block_table), _p(seq_lens), _p(query_start_loc), nseq - num_decode_seqs,
+                                          num_decode_seqs, max_q_len, block_table.stride(0), num_q_heads, hkv,
+                                          head_dim, ps, float(scale), int(window or 0), _p(sink), st),
+                  "attn_prefill_win")
+            sm100._count()
+        return out
     check(_L().gllm_seq_window_attention(_p(q), _p(k_cache), _p(v_cache), _p(block_table), block_table.stride(0),
                                          _p(query_start_loc), _p(positions), t, seq_lens.shape[0], float(scale),
                                          num_q_heads, k_cache.shape[1], head_dim, int(window or 0), _p(sink), _p(out),
@@ -138,10 +164,13 @@ def selective_scan(xc, dt_raw, proj, xz, a, d_skip, dt_bias, ssm_state, rec_slot
     assert xc.is_contiguous() and dt_raw.is_contiguous() and proj.stride(1) == 1 and xz.stride(1) == 1
     assert a.dtype == torch.float32 and a.is_contiguous()
     out = torch.empty_like(xc)
+    # long chunks of few sequences: 4 threads per channel (more warps in flight); decode-like batches: 1
+    nseq = seq_lens.shape[0]
+    parts = 4 if (nstate % 4 == 0 and nstate >= 8 and xc.shape[0] >= 16 * nseq and nseq * channels < (1 << 20)) else 1
     check(_L().gllm_seq_selective_scan(_p(xc), _p(dt_raw), _p(proj), proj.stride(0), _p(xz), xz.stride(0), _p(a),
                                        _p(d_skip), _p(dt_bias), _p(ssm_state), _p(rec_slots), _p(seq_lens),
                                        _p(query_start_loc), seq_lens.shape[0], channels, nstate, dt_rank, _p(out),
-                                       _f32(xc), stream_ptr()), "seq_selective_scan")
+                                       _f32(xc), parts, stream_ptr()), "seq_selective_scan")
     sm100._count()
     return out
 

@@ -76,6 +76,60 @@ def test_kernels_against_unfused_ops(dt, tol):
         assert torch.equal(S.relu2(xz), ref.relu2(xz))
 
 
+@pytest.mark.parametrize("dt,tol", [(torch.float32, 2e-5), (torch.bfloat16, 2e-2)])
+@pytest.mark.parametrize("N,C", [(16, 96), (24, 100), (8, 64), (40, 32)])
+def test_scan_and_conv_on_long_chunks(dt, tol, N, C):
+    """few long sequences take the 4-threads-per-channel scan and (bf16, channels % 8 == 0) the vector convolution"""
+    from gllm_b200.ops import ref, sm100_seq as S
+    torch.manual_seed(2)
+    qlens, ctx, R, taps = [70, 33], [0, 9], 6, 4
+    Tt = sum(qlens)
+    qsl = torch.tensor([0, 70, 103], dtype=torch.int32, device=DEV)
+    sl = torch.tensor([c + q for c, q in zip(ctx, qlens)], dtype=torch.int32, device=DEV)
+    rs = torch.tensor([1, 0], dtype=torch.int32, device=DEV)
+    xz = torch.randn(Tt, 2 * C, device=DEV).to(dt)
+    cw, cb = torch.randn(C, taps, device=DEV), torch.randn(C, device=DEV)
+    cs = torch.randn(3, taps - 1, C, device=DEV).to(dt)
+    cs2 = cs.clone()
+    c1 = S.causal_conv_silu(xz, C, cw, cb, cs, rs, sl, qsl)
+    c2 = ref.causal_conv_silu(xz, C, cw, cb, cs2, rs, sl, qsl)
+    assert close(c1, c2, tol) and torch.equal(cs, cs2)
+    proj, dtr = torch.randn(Tt, R + 2 * N, device=DEV).to(dt), torch.randn(Tt, C, device=DEV).to(dt)
+    A, Dk, db = -torch.rand(C, N, device=DEV) * 2, torch.randn(C, device=DEV), torch.randn(C, device=DEV)
+    ss = torch.randn(3, N, C, device=DEV)
+    ss2 = ss.clone()
+    y1 = S.selective_scan(c2, dtr, proj, xz, A, Dk, db, ss, rs, sl, qsl, C, N, R)
+    y2 = ref.selective_scan(c2, dtr, proj, xz, A, Dk, db, ss2, rs, sl, qsl, C, N, R)
+    assert close(y1, y2, tol) and close(ss, ss2, 1e-5)
+
+
+@pytest.mark.parametrize("D", [64, 128])
+def test_window_and_sink_on_the_tensor_core_attention(D):
+    """decode rows first, then prompt portions; contexts over several 64-key tiles; windows that end inside, at
+    and beyond tile and page borders."""
+    from gllm_b200.ops import ref, sm100_seq as S
+    torch.manual_seed(1)
+    bf, H, G, ps = torch.bfloat16, 8, 2, 16
+    qlens, ctx = [1, 1, 1, 70, 5, 200], [0, 63, 300, 130, 64, 0]
+    B, Tt = len(qlens), sum(qlens)
+    qsl = torch.tensor([0] + torch.tensor(qlens).cumsum(0).tolist(), dtype=torch.int32, device=DEV)
+    sl = torch.tensor([c + q for c, q in zip(ctx, qlens)], dtype=torch.int32, device=DEV)
+    npp = 20
+    bt = torch.randperm(B * npp)[: B * npp].reshape(B, npp).to(torch.int32).to(DEV)
+    kshape = ref.kv_cache_shape(B * npp + 1, G, D, ps)
+    kc, vc = torch.randn(kshape, device=DEV).to(bf), torch.randn(kshape, device=DEV).to(bf)
+    pos = torch.cat([torch.arange(c, c + q) for c, q in zip(ctx, qlens)]).to(torch.int32).to(DEV)
+    q = torch.randn(Tt, H * D, device=DEV).to(bf)
+    sink = torch.randn(H, device=DEV) * 2
+    for wn, sk in ((72, sink), (64, sink), (65, None), (1, sink), (16, None), (None, sink), (None, None), (250, sink)):
+        want = ref.window_attention(q, kc, vc, bt, sl, qsl, D ** -0.5, H, D, wn, sk)
+        got = S.window_attention(q, kc, vc, bt, sl, qsl, pos, D ** -0.5, H, D, wn, sk, num_decode_seqs=3,
+                                 max_q_len=max(qlens))
+        plain = S.window_attention(q, kc, vc, bt, sl, qsl, pos, D ** -0.5, H, D, wn, sk, simt=True)
+        assert close(got, want, 2e-2), (D, wn, sk is not None)
+        assert close(plain, want, 2e-2), (D, wn, sk is not None)
+
+
 @pytest.fixture(scope="module")
 def models():
     out = {}
@@ -94,6 +148,19 @@ def test_chunked_and_decoded_match_oracle(models, name, dtype):
     s = U.session(path, dtype=dtype, device=DEV)
     for k, cuts in enumerate(([len(t)], [], [2, 2, 3, 17, 2], [30])):
         assert U.rel_err(U.run_chunks(s, "r%d" % k, t, cuts), want) < TOLS[dtype], cuts
+
+
+def test_engine_on_the_tensor_core_attention_path():
+    cfg = U.make_config([U.with_mlp(U.attn(heads=4, kv_heads=2, dim=64, window=40, scale=0.125), ff=96),
+                         U.mamba(inner=64, state=16, dt_rank=8, conv=4),
+                         U.attn(heads=2, kv_heads=1, dim=128, window=70, scale=0.09)], width=64, loop=(0, 2, 2))
+    w = U.random_weights(cfg, seed=77)
+    path = U.save_model(cfg, w)
+    t = toks(150, cfg["vocab"], 4)
+    want = U.expected_logits(cfg, w, t)
+    s = U.session(path, dtype="bfloat16", device=DEV, max_tokens=512, page_size=16)
+    for k, cuts in enumerate(([len(t)], [100] + [1] * 50, [2, 62, 3, 64, 17, 2])):
+        assert U.rel_err(U.run_chunks(s, "r%d" % k, t, cuts), want) < TOLS["bfloat16"], cuts
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
