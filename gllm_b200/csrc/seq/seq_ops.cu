@@ -228,39 +228,6 @@ __global__ void conv_silu_kernel(const T* __restrict__ xz, long ldxz, int C, con
   out[(size_t)t * C + c] = from_f<T>(acc / (1.0f + expf(-acc)));
 }
 
-// bf16, C % 8 == 0: eight channels per thread, 16-byte loads and stores
-__global__ void conv_silu_vec8_kernel(const __nv_bfloat16* __restrict__ xz, long ldxz, int C,
-                                      const float* __restrict__ w, const float* __restrict__ b, int taps,
-                                      const __nv_bfloat16* __restrict__ state, const int* __restrict__ rec_slots,
-                                      const int* __restrict__ seq_lens, const int* __restrict__ qsl, int nseq,
-                                      __nv_bfloat16* __restrict__ out) {
-  const int t = blockIdx.x;
-  const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
-  if (c >= C) return;
-  const int s = find_seq(qsl, nseq, t);
-  const int q0 = qsl[s], n = qsl[s + 1] - q0;
-  const bool carried = state != nullptr && (seq_lens[s] - n) > 0;
-  const __nv_bfloat16* st = carried ? state + (size_t)rec_slots[s] * (taps > 1 ? taps - 1 : 1) * C : nullptr;
-  const int li = t - q0;
-  float acc[8];
-#pragma unroll
-  for (int e = 0; e < 8; ++e) acc[e] = b[c + e];
-  for (int j = 0; j < taps; ++j) {
-    const int src = li - (taps - 1) + j;
-    uint4 raw = make_uint4(0u, 0u, 0u, 0u);
-    if (src >= 0) raw = *reinterpret_cast<const uint4*>(xz + (size_t)(q0 + src) * ldxz + c);
-    else if (carried) raw = *reinterpret_cast<const uint4*>(st + (size_t)(taps - 1 + src) * C + c);
-    const __nv_bfloat16* v = reinterpret_cast<const __nv_bfloat16*>(&raw);
-#pragma unroll
-    for (int e = 0; e < 8; ++e) acc[e] = fmaf(w[(size_t)(c + e) * taps + j], __bfloat162float(v[e]), acc[e]);
-  }
-  uint4 o;
-  __nv_bfloat16* ov = reinterpret_cast<__nv_bfloat16*>(&o);
-#pragma unroll
-  for (int e = 0; e < 8; ++e) ov[e] = __float2bfloat16_rn(acc[e] / (1.0f + expf(-acc[e])));
-  *reinterpret_cast<uint4*>(out + (size_t)t * C + c) = o;
-}
-
 // after the convolution: state <- the last taps - 1 inputs of the sequence (shifting in what the chunk brought)
 template <typename T>
 __global__ void conv_state_update_kernel(const T* __restrict__ xz, long ldxz, int C, int taps, T* __restrict__ state,
@@ -527,16 +494,9 @@ GLLM_EXPORT int gllm_seq_conv_silu(const void* xz, long ldxz, int ntok, int nseq
                                                              (const int*)rec_slots, (const int*)seq_lens,
                                                              (const int*)qsl);
   } else {
-    const bool vec = C % 8 == 0 && ldxz % 8 == 0 && ((uintptr_t)xz % 16) == 0 && ((uintptr_t)out % 16) == 0 &&
-                     (state == nullptr || (uintptr_t)state % 16 == 0);
-    if (vec)
-      conv_silu_vec8_kernel<<<dim3(ntok, (C / 8 + 127) / 128), 128, 0, st>>>(
-          (const __nv_bfloat16*)xz, ldxz, C, (const float*)w, (const float*)b, taps, (const __nv_bfloat16*)state,
-          (const int*)rec_slots, (const int*)seq_lens, (const int*)qsl, nseq, (__nv_bfloat16*)out);
-    else
-      conv_silu_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>(
-          (const __nv_bfloat16*)xz, ldxz, C, (const float*)w, (const float*)b, taps, (const __nv_bfloat16*)state,
-          (const int*)rec_slots, (const int*)seq_lens, (const int*)qsl, nseq, (__nv_bfloat16*)out);
+    conv_silu_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>(
+        (const __nv_bfloat16*)xz, ldxz, C, (const float*)w, (const float*)b, taps, (const __nv_bfloat16*)state,
+        (const int*)rec_slots, (const int*)seq_lens, (const int*)qsl, nseq, (__nv_bfloat16*)out);
     if (state != nullptr && taps > 1)
       conv_state_update_kernel<__nv_bfloat16><<<sgrid, 128, 0, st>>>(
           (const __nv_bfloat16*)xz, ldxz, C, taps, (__nv_bfloat16*)state, (const int*)rec_slots, (const int*)seq_lens,

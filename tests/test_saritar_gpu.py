@@ -79,7 +79,7 @@ def test_kernels_against_unfused_ops(dt, tol):
 @pytest.mark.parametrize("dt,tol", [(torch.float32, 2e-5), (torch.bfloat16, 2e-2)])
 @pytest.mark.parametrize("N,C", [(16, 96), (24, 100), (8, 64), (40, 32)])
 def test_scan_and_conv_on_long_chunks(dt, tol, N, C):
-    """few long sequences take the 4-threads-per-channel scan and (bf16, channels % 8 == 0) the vector convolution"""
+    """few long sequences take the 4-threads-per-channel scan"""
     from gllm_b200.ops import ref, sm100_seq as S
     torch.manual_seed(2)
     qlens, ctx, R, taps = [70, 33], [0, 9], 6, 4
