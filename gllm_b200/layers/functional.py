@@ -166,3 +166,73 @@ def relu2(x):
     if x.is_cuda:
         return _seq().relu2(x)
     return ref.relu2(x)
+
+
+# -- norm-after-sum blocks, rotary chunk attention, matrix-state recurrences, routed feed-forward (csrc/seq) ---
+def postnorm(x, y, alpha, w, eps, out_dtype):
+    """x <- rms(alpha * x + y) * w in place on the fp32 stream; returns x in the compute dtype."""
+    if x.is_cuda:
+        return _seq().postnorm(x, y, alpha, w, eps, out_dtype)
+    return ref.postnorm(x, y, alpha, w, eps, out_dtype)
+
+
+def qk_norm_rope_kv_write(qkv, num_heads, num_kv_heads, dim, v_dim, q_norm_w, k_norm_w, eps, positions, rot_dims,
+                          rot_base, k_cache, v_cache, slots):
+    fn = _seq().qk_norm_rope_kv_write if qkv.is_cuda else ref.qk_norm_rope_kv_write
+    return fn(qkv, num_heads, num_kv_heads, dim, v_dim, q_norm_w, k_norm_w, eps, positions, rot_dims, rot_base,
+              k_cache, v_cache, slots)
+
+
+def masked_attention(q, k_cache, v_cache, inp, scale, num_q_heads, head_dim, v_dim, window=None, chunk=None, sink=None,
+                     out_scale=1.0, out=None):
+    """Paged causal attention with a sliding window and / or a chunk mask, values of their own width."""
+    if q.is_cuda:
+        return _seq().window_attention(q, k_cache, v_cache, inp.block_table, inp.seq_lens, inp.query_start_loc,
+                                       inp.positions, scale, num_q_heads, head_dim, window, sink,
+                                       num_decode_seqs=inp.padded_tokens or inp.num_decode_seqs,
+                                       max_q_len=inp.max_q_len, chunk=chunk, v_dim=v_dim, out_scale=out_scale, out=out)
+    return ref.window_attention(q, k_cache, v_cache, inp.block_table, inp.seq_lens, inp.query_start_loc, scale,
+                                num_q_heads, head_dim, window, sink, chunk=chunk, v_dim=v_dim, out_scale=out_scale,
+                                out=out)
+
+
+def linear_state_scan(q, k, v, beta, a, neg_a, dt_bias, decay, state, inp, heads, qk_heads, dim, v_dim, silu_in,
+                      unit_qk, q_scale, delta):
+    slots = inp.rec_slots if state is not None else None
+    fn = _seq().linear_state_scan if q.is_cuda else ref.linear_state_scan
+    return fn(q, k, v, beta, a, neg_a, dt_bias, decay, state, slots, inp.seq_lens, inp.query_start_loc, heads,
+              qk_heads, dim, v_dim, silu_in, unit_qk, q_scale, delta)
+
+
+def gated_group_norm(o, gate, w, group, eps, act, out_scale=1.0, out=None, out_dtype=None):
+    fn = _seq().gated_group_norm if o.is_cuda else ref.gated_group_norm
+    return fn(o, gate, w, group, eps, act, out_scale, out, out_dtype)
+
+
+def silu_mul(gu):
+    if gu.is_cuda:
+        return _seq().silu_mul(gu)
+    return ref.silu_mul(gu)
+
+
+def router_topk(h, w, top_k):
+    if h.is_cuda:
+        return _seq().router_topk(h, w, top_k)
+    return ref.router_topk(h, w, top_k)
+
+
+def routed_experts(h, w13, w2, weights, ids, interleaved):
+    """sum_k weights[t, k] * expert_{ids[t, k]}(h[t]); w13 [E, 2F, W] = [gate rows ; up rows] (per-64 interleaved
+    when `interleaved`: the grouped tcgen05 GEMM's layout), w2 [E, W, F]."""
+    if h.is_cuda:
+        if interleaved:
+            from gllm_b200.ops import sm100_moe
+            return sm100_moe.fused_experts(h, w13, w2, weights, ids, None)
+        return _seq().routed_experts(h, w13, w2, weights, ids)
+    return ref.fused_experts(h, w13, w2, weights, ids, None)
+
+
+def softcap(z, cap):
+    if z.is_cuda:
+        return _seq().softcap(z, cap)
+    return ref.softcap(z, cap)

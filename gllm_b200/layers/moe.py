@@ -240,3 +240,31 @@ class SparseMoeBlock(nn.Module):
 
 def make_moe_block(spec, layer_id: int, device):
     return SparseMoeBlock(spec, layer_id, device)
+
+
+class SelectedSoftmaxMoE(nn.Module):
+    """Routed feed-forward without shared experts: fp32 router logits, the `top_k` largest are chosen and weighted
+    by the softmax over the chosen logits only; every expert is down(silu(gate h) * (up h)). One GPU. On CUDA in
+    bf16 with ff % 64 == 0 and hidden % 128 == 0 the experts run as the grouped tcgen05 GEMM pair of `FusedMoE`
+    (per-64 interleaved gate/up rows), otherwise on the plain per-slot kernels (true fp32 for fp32 weights)."""
+
+    def __init__(self, num_experts: int, top_k: int, hidden: int, ff: int, dtype, device):
+        super().__init__()
+        assert 1 <= top_k <= num_experts, (top_k, num_experts)
+        self.num_experts, self.top_k, self.hidden, self.ff = num_experts, top_k, hidden, ff
+        self.router_w = _param(num_experts, hidden, dtype=dtype, device=device)
+        self.w13 = _param(num_experts, 2 * ff, hidden, dtype=dtype, device=device)
+        self.w2 = _param(num_experts, hidden, ff, dtype=dtype, device=device)
+        self.interleaved = torch.device(device).type == "cuda" and dtype == torch.bfloat16 and ff % 64 == 0 and \
+            hidden % 128 == 0
+
+    def forward(self, h: torch.Tensor) -> torch.Tensor:
+        w, ids = Fn.router_topk(h, self.router_w, self.top_k)
+        return Fn.routed_experts(h, self.w13, self.w2, w, ids, self.interleaved)
+
+    def load_expert(self, e: int, gate: torch.Tensor, up: torch.Tensor, down: torch.Tensor):
+        gu = torch.cat([gate, up], dim=0)
+        if self.interleaved:
+            gu = ref.interleave_gate_up(gu, 64)
+        self.w13.data[e].copy_(gu)
+        self.w2.data[e].copy_(down)

@@ -50,7 +50,31 @@ class HybridCache:
       {"kind": "ssm", "channels", "nstate", "taps"}  -> conv_state[r] [slots, taps - 1, channels] (compute dtype) and
                                                         ssm_state[r] [slots, nstate, channels] fp32, indexed by the
                                                         sequence's state slot (`Sequence.rec_slot`)
+      {"kind": "kv", ..., "vdim"}                    -> values of their own width: v_cache[r] is shaped for vdim
+      {"kind": "linear", "heads", "dim", "vdim", "taps", "channels"}
+                                                     -> ssm_state[r] [slots, heads, dim, vdim] fp32 (one matrix per
+                                                        head) and, with taps > 1, conv_state[r] [slots, taps - 1,
+                                                        channels]
+      {"kind": "multi", "kv": entry | None, "rec": entry | None}   -> a run that keeps both pages and state
     Slot contents are never cleared on re-use: the kernels start from zeros for a chunk at position 0."""
+
+    @staticmethod
+    def _parts(e):
+        """-> (paged entry | None, recurrent entry | None)"""
+        if e["kind"] == "multi":
+            return e.get("kv"), e.get("rec")
+        if e["kind"] == "kv":
+            return e, None
+        if e["kind"] in ("ssm", "linear"):
+            return None, e
+        raise ValueError(e["kind"])
+
+    @staticmethod
+    def _rec_shapes(e):
+        """-> (conv taps shape per slot, state shape per slot)"""
+        if e["kind"] == "ssm":
+            return (max(e["taps"] - 1, 1), e["channels"]), (e["nstate"], e["channels"])
+        return (max(e["taps"] - 1, 1), max(e["channels"], 1)), (e["heads"], e["dim"], e["vdim"])
 
     def __init__(self, layout: List[dict], num_pages: int, page_size: int, num_slots: int, dtype: torch.dtype, device):
         self.layout, self.num_pages, self.page_size, self.num_slots = layout, num_pages, page_size, num_slots
@@ -59,15 +83,16 @@ class HybridCache:
         self.k_cache, self.v_cache, self.conv_state, self.ssm_state = [], [], [], []
         for e in layout:
             k = v = cs = ss = None
-            if e["kind"] == "kv":
-                shape = kv_cache_shape(num_pages, e["heads"], e["dim"], page_size)
-                k = torch.zeros(shape, dtype=dtype, device=device)
-                v = torch.zeros(shape, dtype=dtype, device=device)
-            elif e["kind"] == "ssm":
-                cs = torch.zeros(num_slots, max(e["taps"] - 1, 1), e["channels"], dtype=dtype, device=device)
-                ss = torch.zeros(num_slots, e["nstate"], e["channels"], dtype=torch.float32, device=device)
-            else:
-                raise ValueError(e["kind"])
+            kv, rec = self._parts(e)
+            if kv is not None:
+                k = torch.zeros(kv_cache_shape(num_pages, kv["heads"], kv["dim"], page_size), dtype=dtype,
+                                device=device)
+                v = torch.zeros(kv_cache_shape(num_pages, kv["heads"], kv.get("vdim", kv["dim"]), page_size),
+                                dtype=dtype, device=device)
+            if rec is not None:
+                cshape, sshape = self._rec_shapes(rec)
+                cs = torch.zeros(num_slots, *cshape, dtype=dtype, device=device)
+                ss = torch.zeros(num_slots, *sshape, dtype=torch.float32, device=device)
             self.k_cache.append(k)
             self.v_cache.append(v)
             self.conv_state.append(cs)
@@ -75,12 +100,20 @@ class HybridCache:
 
     @staticmethod
     def bytes_per_page(layout, page_size: int, dtype_bytes: int) -> int:
-        return sum(2 * page_size * e["heads"] * e["dim"] * dtype_bytes for e in layout if e["kind"] == "kv")
+        kvs = [HybridCache._parts(e)[0] for e in layout]
+        return sum(page_size * e["heads"] * (e["dim"] + e.get("vdim", e["dim"])) * dtype_bytes
+                   for e in kvs if e is not None)
 
     @staticmethod
     def bytes_per_slot(layout, dtype_bytes: int) -> int:
-        return sum(max(e["taps"] - 1, 1) * e["channels"] * dtype_bytes + 4 * e["nstate"] * e["channels"]
-                   for e in layout if e["kind"] == "ssm")
+        import math
+        total = 0
+        for e in layout:
+            rec = HybridCache._parts(e)[1]
+            if rec is not None:
+                cshape, sshape = HybridCache._rec_shapes(rec)
+                total += math.prod(cshape) * dtype_bytes + 4 * math.prod(sshape)
+        return total
 
 
 class MemoryManager:

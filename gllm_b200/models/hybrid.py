@@ -1,6 +1,15 @@
-"""Layer-list decoder: a stack whose every layer names its own mixer (windowed sink attention, Mamba-1 scan) and
-an optional feed-forward, with sandwich norms around each sublayer, an fp32 residual stream and an optional loop
-that re-runs a span of layers with shared weights. Architecture `Saritar` is built from it.
+"""Layer-list decoder: a stack whose every layer names its own mixer and an optional feed-forward, over an fp32
+residual stream. Two block forms: sandwich norms around each sublayer with an optional loop that re-runs a span of
+layers with shared weights (architecture `Saritar`: windowed sink attention and Mamba-1 mixers, squared-ReLU
+feed-forward), and norm-after-sum blocks (architecture `Femolix`: gated delta rule mixers and parallel mixers of
+chunk-masked rotary attention beside constant-decay linear attention, gated SiLU feed-forward, dense or routed, capped
+logits):
+
+    x = embed[token]
+    per layer:  x <- rms(alpha x + mixer(x)) * n1 ;  x <- rms(alpha x + ff(x)) * n2     (second line only with a ff)
+    logits = cap * tanh(head @ (rms(x) * final_norm) / cap)
+
+The sandwich form:
 
     x = embed[token] * embed_scale                                   (fp32 from here on)
     per layer:  x += rms(mixer(rms(x) * n1)) * n1b ;  x += rms(ff(rms(x) * n2)) * n2b   (second line only with a ff)
@@ -12,9 +21,13 @@ Dataflow on the device: every residual update is ONE kernel that applies the pos
 optionally adds the embedding (loop re-entry) and emits the next sublayer's pre-normed input in the compute dtype
 (`Fn.resid_norm`), so the stream is read and written once per sublayer.
 
+In the norm-after-sum form one kernel per sublayer (`Fn.postnorm`) scales the stream, adds the sublayer's output,
+norms, writes the stream back and emits it in the compute dtype for the next sublayer.
+
 config.json keys read here: architecture, vocab, width, embedding.scale, norm.eps, loop.{start,stop,times},
-layers[i].{type, mixer{...}, mlp{kind, ff} | null}, optional torch_dtype. Tensor names: embed, head, final.norm,
-l<i>.norm1|norm1b|norm2|norm2b, l<i>.mix.*, l<i>.mlp.up|down.
+postln_alpha, logit_softcap, layers[i].{type, mixer{...}, mlp{kind, ff | expert.ff, router.{experts, top}} | null},
+optional torch_dtype. Tensor names: embed, head, final.norm, l<i>.norm1|norm1b|norm2|norm2b, l<i>.mix.*,
+l<i>.mlp.up|down|gate|router|e<j>.{gate,up,down}.
 """
 from __future__ import annotations
 
@@ -25,8 +38,11 @@ import torch
 from torch import nn
 
 from gllm_b200.layers import functional as Fn
+from gllm_b200.layers.linear_attention import DecayLinearCore, GatedDeltaCore
+from gllm_b200.layers.moe import SelectedSoftmaxMoE
+from gllm_b200.layers.parallel_mixer import CoreMixer
 from gllm_b200.layers.ssm import Mamba1Mixer
-from gllm_b200.layers.window_attention import SinkWindowAttention
+from gllm_b200.layers.window_attention import RotaryChunkCore, SinkWindowAttention
 from gllm_b200.parallel import state as ps
 
 _DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32, torch.bfloat16: torch.bfloat16,
@@ -45,6 +61,10 @@ class HybridSpec:
     loop_stop: int = 0
     loop_times: int = 1
     dtype: torch.dtype = torch.bfloat16
+    block: str = "sandwich"            # "sandwich": x += post(f(pre(x))) | "postnorm": x <- norm(alpha x + f(x))
+    resid_alpha: float = 1.0
+    logit_softcap: float = 0.0         # 0: none
+    ff_act: str = "relu2"              # "relu2": down(relu(up h)^2) | "silu_gate": down(silu(gate h) * up h)
     eos_token_id: Optional[object] = None
     use_mla: bool = False
     quant: Optional[str] = None
@@ -64,6 +84,17 @@ def spec_saritar(cfg) -> HybridSpec:
                       rms_eps=float(cfg["norm"]["eps"]), embed_scale=float((cfg.get("embedding") or {}).get("scale", 1.0)),
                       layers=[dict(x) for x in cfg["layers"]], loop_start=int(loop.get("start", 0)),
                       loop_stop=int(loop.get("stop", 0)), loop_times=int(loop.get("times", 1)), dtype=_DTYPES[dt],
+                      eos_token_id=cfg.get("eos_token_id"))
+
+
+def spec_femolix(cfg) -> HybridSpec:
+    dt = cfg.get("torch_dtype", cfg.get("dtype", "bfloat16"))
+    if dt not in _DTYPES:
+        raise ValueError(f"unsupported dtype {dt} for this architecture (bfloat16 | float32)")
+    return HybridSpec(arch="femolix", hidden_size=int(cfg["width"]), vocab_size=int(cfg["vocab"]),
+                      rms_eps=float(cfg["norm"]["eps"]), embed_scale=1.0, layers=[dict(x) for x in cfg["layers"]],
+                      dtype=_DTYPES[dt], block="postnorm", resid_alpha=float(cfg.get("postln_alpha", 1.0)),
+                      logit_softcap=float(cfg.get("logit_softcap") or 0.0), ff_act="silu_gate",
                       eos_token_id=cfg.get("eos_token_id"))
 
 
@@ -98,7 +129,46 @@ def make_mixer(kind: str, m: dict, spec: HybridSpec, device):
                                    int(window) if window is not None else None, spec.rms_eps, dt, device)
     if kind == "mamba1":
         return Mamba1Mixer(h, int(m["inner"]), int(m["state"]), int(m["dt_rank"]), int(m["conv"]), dt, device)
+    if kind == "delta":
+        core = GatedDeltaCore(int(m["heads"]), int(m.get("kv_heads", m["heads"])), int(m["dim"]),
+                              int(m.get("vdim", m["dim"])), int(m.get("conv", 1)), spec.rms_eps, dt, device)
+        return CoreMixer(h, [core], [""], [1.0], dt, device)
+    if kind == "parallel":
+        l, r = m["left"], m["right"]
+        rot, mask = l.get("rot") or {}, l.get("mask") or {}
+        left = RotaryChunkCore(int(l["heads"]), int(l.get("kv_heads", l["heads"])), int(l["dim"]),
+                               int(l.get("vdim", l["dim"])), float(l["scale"]), int(rot.get("dims", 0)),
+                               float(rot.get("base", 10000.0)), int(mask["size"]) if mask.get("size") else None, None,
+                               spec.rms_eps, dt, device)
+        right = DecayLinearCore(int(r["heads"]), int(r["dim"]), int(r.get("vdim", r["dim"])), list(r["decay"]),
+                                spec.rms_eps, dt, device)
+        return CoreMixer(h, [left, right], ["left", "right"], [float(m.get("left_scale", 1.0)),
+                                                               float(m.get("right_scale", 1.0))], dt, device)
     raise ValueError(f"unknown mixer type {kind!r}")
+
+
+class GatedMLP(nn.Module):
+    """down(silu(gate h) * (up h)); gate and up rows share one GEMM."""
+
+    def __init__(self, hidden: int, ff: int, dtype, device):
+        super().__init__()
+        self.ff = ff
+        self.gate_up_w = nn.Parameter(torch.zeros(2 * ff, hidden, dtype=dtype, device=device), requires_grad=False)
+        self.down_w = nn.Parameter(torch.zeros(hidden, ff, dtype=dtype, device=device), requires_grad=False)
+
+    def forward(self, h):
+        return Fn.linear_any(Fn.silu_mul(Fn.linear_any(h, self.gate_up_w)), self.down_w)
+
+
+def make_ff(mlp: dict, spec: HybridSpec, device):
+    h, dt = spec.hidden_size, spec.dtype
+    kind = mlp.get("kind", "dense")
+    if kind == "dense":
+        return (GatedMLP if spec.ff_act == "silu_gate" else Relu2MLP)(h, int(mlp["ff"]), dt, device)
+    if kind == "moe" and spec.ff_act == "silu_gate":
+        return SelectedSoftmaxMoE(int(mlp["router"]["experts"]), int(mlp["router"]["top"]), h,
+                                  int(mlp["expert"]["ff"]), dt, device)
+    raise ValueError(f"unknown feed-forward kind {kind!r}")
 
 
 class HybridLayer(nn.Module):
@@ -112,14 +182,13 @@ class HybridLayer(nn.Module):
 
         self.layer_id = layer_id
         self.kind = L["type"]
-        self.norm1_w, self.norm1b_w = norm(), norm()
+        sandwich = spec.block == "sandwich"
+        self.norm1_w, self.norm1b_w = norm(), (norm() if sandwich else None)
         self.mixer = make_mixer(L["type"], L["mixer"], spec, device)
         mlp = L.get("mlp")
         if mlp is not None:
-            if mlp.get("kind", "dense") != "dense":
-                raise ValueError(f"unknown feed-forward kind {mlp.get('kind')!r}")
-            self.norm2_w, self.norm2b_w = norm(), norm()
-            self.mlp = Relu2MLP(h, int(mlp["ff"]), dt, device)
+            self.norm2_w, self.norm2b_w = norm(), (norm() if sandwich else None)
+            self.mlp = make_ff(mlp, spec, device)
         else:
             self.mlp = None
 
@@ -139,7 +208,7 @@ class HybridLM(nn.Module):
         self.final_norm_w = nn.Parameter(torch.ones(h, dtype=dt, device=device), requires_grad=False)
         self.lm_head_w = nn.Parameter(torch.zeros(spec.vocab_size, h, dtype=dt, device=device), requires_grad=False)
         self.runs = layer_runs(spec.num_layers, spec.loop_start, spec.loop_stop, spec.loop_times)
-        self.has_state = any(not l.mixer.uses_pages for l in self.layers)
+        self.has_state = any(getattr(l.mixer, "uses_state", not l.mixer.uses_pages) for l in self.layers)
         self.has_pages = any(l.mixer.uses_pages for l in self.layers)
         self.trace: Optional[list] = None     # debugging: when a list, the stream after every layer run is appended
 
@@ -157,6 +226,8 @@ class HybridLM(nn.Module):
     # -- forward ----------------------------------------------------------------------------------
     def forward(self, inp, cache, tpc=None, hidden=None, residual=None, **_):
         spec, eps, dt = self.spec, self.spec.rms_eps, self.spec.dtype
+        if spec.block == "postnorm":
+            return self._forward_postnorm(inp, cache), None
         x0 = Fn.embedding_scaled(inp.tokens, self.embed_w, spec.embed_scale)
         x = x0.clone() if any(a for _, a in self.runs) else x0
         n = len(self.runs)
@@ -181,9 +252,23 @@ class HybridLM(nn.Module):
                 h = Fn.resid_norm(x, y, post, add, w_pre, eps, dt)
         return h, None
 
+    def _forward_postnorm(self, inp, cache):
+        spec, eps, dt, alpha = self.spec, self.spec.rms_eps, self.spec.dtype, self.spec.resid_alpha
+        x = Fn.embedding_scaled(inp.tokens, self.embed_w, spec.embed_scale)
+        h = x if dt == torch.float32 else x.to(dt)       # exact: the table holds compute-dtype values
+        for r, (li, _) in enumerate(self.runs):
+            L = self.layers[li]
+            h = Fn.postnorm(x, L.mixer(inp, h, cache, r), alpha, L.norm1_w, eps, dt)
+            if L.mlp is not None:
+                h = Fn.postnorm(x, L.mlp(h), alpha, L.norm2_w, eps, dt)
+            if self.trace is not None:
+                self.trace.append(x.clone())
+        return Fn.resid_norm(x, None, None, None, self.final_norm_w, eps, dt)
+
     def compute_logits(self, inp, hidden, tpc=None, all_rows: bool = False, local: bool = False):
         rows = hidden if all_rows else hidden.index_select(0, inp.logits_idx.long())
-        return Fn.linear_any(rows, self.lm_head_w)
+        z = Fn.linear_any(rows, self.lm_head_w)
+        return Fn.softcap(z, self.spec.logit_softcap) if self.spec.logit_softcap > 0 else z
 
     # -- weights ----------------------------------------------------------------------------------
     def process_weights(self):
@@ -204,12 +289,18 @@ class HybridLM(nn.Module):
                 p.data.copy_(torch.rand(p.shape, generator=g) * 2.0 - 3.0)
             elif name.endswith("d_skip"):
                 p.data.fill_(1.0)
+            elif name.endswith("neg_a"):
+                p.data.copy_(-torch.exp(torch.rand(p.shape, generator=g) * 2.0 - 1.0))
+            elif name.endswith("dt_bias"):
+                p.data.copy_(torch.rand(p.shape, generator=g) * 2.0 - 3.0)
+            elif name.endswith("conv_b") and "cores" in name:
+                p.data.zero_()
             elif name.endswith("sink") or name.endswith("conv_b"):
                 rnd(p, 0.5)
             elif name.endswith("conv_w"):
                 rnd(p, 0.4)
-            elif p.dim() == 2:
-                rnd(p, 1.0 / max(p.shape[1], 1) ** 0.5)
+            elif p.dim() >= 2:
+                rnd(p, 1.0 / max(p.shape[-1], 1) ** 0.5)
             else:
                 rnd(p, 0.02)
 
@@ -224,7 +315,8 @@ class HybridLM(nn.Module):
         for n, L in enumerate(self.layers):
             pre = f"l{L.layer_id}."
             put(L.norm1_w, reader.get(pre + "norm1"))
-            put(L.norm1b_w, reader.get(pre + "norm1b"))
+            if L.norm1b_w is not None:
+                put(L.norm1b_w, reader.get(pre + "norm1b"))
             m = L.mixer
             mp = pre + "mix."
             if isinstance(m, SinkWindowAttention):
@@ -245,11 +337,24 @@ class HybridLM(nn.Module):
                 put(m.a, -torch.exp(reader.get(mp + "A_log").float()))
                 put(m.d_skip, reader.get(mp + "D").float())
                 put(m.o_w, reader.get(mp + "o"))
+            elif isinstance(m, CoreMixer):
+                m.load(reader, mp, put)
             if L.mlp is not None:
                 put(L.norm2_w, reader.get(pre + "norm2"))
-                put(L.norm2b_w, reader.get(pre + "norm2b"))
-                put(L.mlp.up_w, reader.get(pre + "mlp.up"))
-                put(L.mlp.down_w, reader.get(pre + "mlp.down"))
+                if L.norm2b_w is not None:
+                    put(L.norm2b_w, reader.get(pre + "norm2b"))
+                f = L.mlp
+                if isinstance(f, SelectedSoftmaxMoE):
+                    put(f.router_w, reader.get(pre + "mlp.router"))
+                    for e in range(f.num_experts):
+                        ep = f"{pre}mlp.e{e}."
+                        f.load_expert(e, reader.get(ep + "gate"), reader.get(ep + "up"), reader.get(ep + "down"))
+                elif isinstance(f, GatedMLP):
+                    put(f.gate_up_w, torch.cat([reader.get(pre + "mlp.gate"), reader.get(pre + "mlp.up")], 0))
+                    put(f.down_w, reader.get(pre + "mlp.down"))
+                else:
+                    put(f.up_w, reader.get(pre + "mlp.up"))
+                    put(f.down_w, reader.get(pre + "mlp.down"))
             if progress is not None:
                 progress(n + 2, total)
         put(self.final_norm_w, reader.get("final.norm"))
@@ -260,3 +365,7 @@ class HybridLM(nn.Module):
 
 def build_saritar(cfg, device):
     return HybridLM(spec_saritar(cfg), device)
+
+
+def build_femolix(cfg, device):
+    return HybridLM(spec_femolix(cfg), device)

@@ -4,7 +4,7 @@ Supported `architectures[0]` values:
   LlamaForCausalLM, Qwen2ForCausalLM, Qwen3ForCausalLM, Qwen2MoeForCausalLM, Qwen3MoeForCausalLM,
   MixtralForCausalLM, ChatGLMModel / ChatGLMForConditionalGeneration, DeepseekV2ForCausalLM,
   DeepseekV3ForCausalLM, Qwen2_5_VLForConditionalGeneration, Qwen3VLForConditionalGeneration,
-  Qwen3VLMoeForConditionalGeneration, Saritar (layer-list decoder, models/hybrid.py).
+  Qwen3VLMoeForConditionalGeneration, Saritar and Femolix (layer-list decoders, models/hybrid.py).
 """
 from __future__ import annotations
 
@@ -166,8 +166,14 @@ def _build_saritar(cfg, device):
     return build_saritar(cfg, device)
 
 
+def _build_femolix(cfg, device):
+    from gllm_b200.models.hybrid import build_femolix
+    return build_femolix(cfg, device)
+
+
 ARCHITECTURES: Dict[str, Callable] = {
     "Saritar": _build_saritar,
+    "Femolix": _build_femolix,
     "LlamaForCausalLM": _build_decoder(spec_llama),
     "MistralForCausalLM": _build_decoder(spec_llama),
     "Qwen2ForCausalLM": _build_decoder(spec_qwen2),

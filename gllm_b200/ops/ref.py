@@ -7,6 +7,7 @@ hand-written kernels in `gllm_b200.ops.sm100`.
 """
 from __future__ import annotations
 
+import math
 from typing import Optional
 
 import torch
@@ -506,13 +507,20 @@ def qk_norm_kv_write(qk: torch.Tensor, num_heads: int, num_kv_heads: int, dim: i
 
 def window_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
                      seq_lens: torch.Tensor, query_start_loc: torch.Tensor, scale: float, num_q_heads: int,
-                     head_dim: int, window: Optional[int], sink: Optional[torch.Tensor]) -> torch.Tensor:
-    """Causal paged attention where position i sees j with 0 <= i - j < window (None: all of the past) and the
-    softmax denominator has one more term exp(sink[h]) that carries no value (None: plain softmax)."""
+                     head_dim: int, window: Optional[int], sink: Optional[torch.Tensor],
+                     chunk: Optional[int] = None, v_dim: Optional[int] = None, out_scale: float = 1.0,
+                     out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Causal paged attention where position i sees j with 0 <= i - j < window (None: all of the past), and, with
+    `chunk`, only j of its own chunk (floor(i / chunk) == floor(j / chunk), counted from position 0); the softmax
+    denominator has one more term exp(sink[h]) that carries no value (None: plain softmax). Values may be wider or
+    narrower than keys (`v_dim`); the result is multiplied by `out_scale` and written to `out` [T, H * v_dim] (any
+    row stride) when given."""
     t = q.shape[0]
     hq, d = num_q_heads, head_dim
+    dv = d if v_dim is None else v_dim
     g = hq // k_cache.shape[1]
-    out = torch.zeros(t, hq * d, dtype=q.dtype, device=q.device)
+    if out is None:
+        out = torch.zeros(t, hq * dv, dtype=q.dtype, device=q.device)
     qsl, sl = query_start_loc.tolist(), seq_lens.tolist()
     for s in range(len(sl)):
         q0, q1 = qsl[s], qsl[s + 1]
@@ -528,11 +536,13 @@ def window_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
         dead = kj > qi
         if window is not None:
             dead = dead | (qi - kj >= window)
+        if chunk is not None:
+            dead = dead | (qi // chunk != kj // chunk)
         att = att.masked_fill(dead.unsqueeze(0), float("-inf"))
         if sink is not None:
             att = torch.cat([att, sink.float().view(hq, 1, 1).expand(hq, ql, 1)], dim=-1)
         p = torch.softmax(att, dim=-1)[..., : sl[s]]
-        out[q0:q1] = torch.einsum("hqk,khd->qhd", p, vv).reshape(ql, hq * d).to(q.dtype)
+        out[q0:q1] = (torch.einsum("hqk,khd->qhd", p, vv).reshape(ql, hq * dv) * out_scale).to(q.dtype)
     return out
 
 
@@ -601,3 +611,137 @@ def selective_scan(xc: torch.Tensor, dt_raw: torch.Tensor, proj: torch.Tensor, x
 def relu2(x: torch.Tensor) -> torch.Tensor:
     r = torch.relu(x.float())
     return (r * r).to(x.dtype)
+
+
+# ----------------------------------------------------------------------------------------------
+# norm-after-sum blocks, rotary q/k norm + cache write, matrix-state linear recurrences (delta rule, constant
+# decay), group norm with a gate, top-k router, plain experts, logit cap (PyTorch forms of csrc/seq/state_ops.cu)
+# ----------------------------------------------------------------------------------------------
+def postnorm(x: torch.Tensor, y: torch.Tensor, alpha: float, w: torch.Tensor, eps: float, out_dtype):
+    """In place on the fp32 stream: x <- rms(alpha * x + y) * w. Returns x in `out_dtype` (x itself for fp32)."""
+    v = alpha * x + y.float()
+    x.copy_(v * torch.rsqrt((v * v).mean(-1, keepdim=True) + eps) * w.float())
+    return x if out_dtype == torch.float32 else x.to(out_dtype)
+
+
+def rotate_half_pairs(x: torch.Tensor, positions: torch.Tensor, rot_dims: int, base: float) -> torch.Tensor:
+    """x [T, heads, D] fp32: entries i and i + rot_dims / 2 (i < rot_dims / 2) turn by positions * base^(-2i/rot_dims);
+    entries from rot_dims on pass through. Angles are formed in fp64."""
+    if rot_dims <= 0:
+        return x
+    half = rot_dims // 2
+    freq = torch.exp2(-(2.0 * torch.arange(half, dtype=torch.float64, device=x.device) / rot_dims) * math.log2(base))
+    ang = positions.to(torch.float64)[:, None] * freq[None, :]
+    c, s = torch.cos(ang).float()[:, None, :], torch.sin(ang).float()[:, None, :]
+    a, b = x[..., :half], x[..., half:rot_dims]
+    return torch.cat([a * c - b * s, b * c + a * s, x[..., rot_dims:]], -1)
+
+
+def qk_norm_rope_kv_write(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, dim: int, v_dim: int, q_norm_w,
+                          k_norm_w, eps: float, positions: torch.Tensor, rot_dims: int, rot_base: float,
+                          k_cache: torch.Tensor, v_cache: torch.Tensor, slots: torch.Tensor) -> torch.Tensor:
+    """qkv [T, >= H*D + G*D + G*Dv] = [queries | keys | values]. Per-head RMS norm of q and k (weights optional),
+    then the rotate-half rotation of both; rotated keys go to the K cache, values as projected to the V cache.
+    Returns the queries [T, H * D]."""
+    t = qkv.shape[0]
+    hd, gd = num_heads * dim, num_kv_heads * dim
+    q = qkv[:, :hd].reshape(t, num_heads, dim).float()
+    k = qkv[:, hd:hd + gd].reshape(t, num_kv_heads, dim).float()
+    v = qkv[:, hd + gd:hd + gd + num_kv_heads * v_dim].reshape(t, num_kv_heads, v_dim)
+    if q_norm_w is not None:
+        q = q * torch.rsqrt((q * q).mean(-1, keepdim=True) + eps) * q_norm_w.float()
+    if k_norm_w is not None:
+        k = k * torch.rsqrt((k * k).mean(-1, keepdim=True) + eps) * k_norm_w.float()
+    q = rotate_half_pairs(q, positions, rot_dims, rot_base)
+    k = rotate_half_pairs(k, positions, rot_dims, rot_base)
+    _cache_rows_write(k_cache, slots, k.to(qkv.dtype))
+    _cache_rows_write(v_cache, slots, v)
+    return q.to(qkv.dtype).reshape(t, hd)
+
+
+def linear_state_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta: Optional[torch.Tensor],
+                      a: Optional[torch.Tensor], neg_a: Optional[torch.Tensor], dt_bias: Optional[torch.Tensor],
+                      decay: Optional[torch.Tensor], state: Optional[torch.Tensor], rec_slots, seq_lens, query_start_loc,
+                      heads: int, qk_heads: int, dim: int, v_dim: int, silu_in: bool, unit_qk: bool, q_scale: float,
+                      delta: bool) -> torch.Tensor:
+    """Matrix-state recurrence per head, fp32, token by token, S [dim, v_dim]:
+        g = exp(neg_a[h] * softplus(a + dt_bias[h]))   (or the constant decay[h])
+        S <- g S;   u = beta * (v - S^T k) with `delta`, else u = v;   S <- S + k u^T;   o = S^T q
+    q, k [T, qk_heads * dim] (head h reads group h // (heads / qk_heads)), v [T, heads * v_dim], beta / a [T, heads].
+    `silu_in`: q, k, v pass SiLU first; `unit_qk`: q and k are scaled to unit length (1e-6 inside the root);
+    q is multiplied by q_scale. state [slots, heads, dim, v_dim] fp32 carries S between chunks (zeros for a chunk
+    that starts at position 0). Returns o [T, heads * v_dim] fp32."""
+    t = q.shape[0]
+    out = torch.zeros(t, heads * v_dim, dtype=torch.float32, device=q.device)
+    qsl, sl = query_start_loc.tolist(), seq_lens.tolist()
+    rep = heads // qk_heads
+    for s in range(len(sl)):
+        q0, q1 = qsl[s], qsl[s + 1]
+        n = q1 - q0
+        if n <= 0:
+            continue
+        qq = q[q0:q1].float().reshape(n, qk_heads, dim)
+        kk = k[q0:q1].float().reshape(n, qk_heads, dim)
+        vv = v[q0:q1].float().reshape(n, heads, v_dim)
+        if silu_in:
+            qq, kk, vv = F.silu(qq), F.silu(kk), F.silu(vv)
+        if unit_qk:
+            qq = qq / torch.sqrt((qq * qq).sum(-1, keepdim=True) + 1e-6)
+            kk = kk / torch.sqrt((kk * kk).sum(-1, keepdim=True) + 1e-6)
+        qq = (qq * q_scale).repeat_interleave(rep, 1)
+        kk = kk.repeat_interleave(rep, 1)
+        if decay is not None:
+            g = decay.float().view(1, heads).expand(n, heads)
+        else:
+            g = torch.exp(neg_a.float() * F.softplus(a[q0:q1].float() + dt_bias.float()))
+        b = torch.sigmoid(beta[q0:q1].float()) if delta else None
+        st = torch.zeros(heads, dim, v_dim, dtype=torch.float32, device=q.device)
+        if state is not None and sl[s] - n > 0:
+            st = state[int(rec_slots[s])].clone()
+        o = torch.empty(n, heads, v_dim, dtype=torch.float32, device=q.device)
+        for i in range(n):
+            st = st * g[i].view(heads, 1, 1)
+            u = vv[i]
+            if delta:
+                u = b[i].view(heads, 1) * (u - torch.einsum("hdv,hd->hv", st, kk[i]))
+            st = st + kk[i].unsqueeze(-1) * u.unsqueeze(1)
+            o[i] = torch.einsum("hdv,hd->hv", st, qq[i])
+        out[q0:q1] = o.reshape(n, heads * v_dim)
+        if state is not None:
+            state[int(rec_slots[s])] = st
+    return out
+
+
+def gated_group_norm(o: torch.Tensor, gate: torch.Tensor, w: torch.Tensor, group: int, eps: float, act: str,
+                     out_scale: float = 1.0, out: Optional[torch.Tensor] = None, out_dtype=None) -> torch.Tensor:
+    """o [T, n] fp32 is RMS-normed over consecutive groups of `group` columns, multiplied by w (w[i % len(w)]) and
+    by act(gate) (act: "silu" | "sigmoid"), times out_scale."""
+    t, n = o.shape
+    x = o.float().reshape(t, n // group, group)
+    x = (x * torch.rsqrt((x * x).mean(-1, keepdim=True) + eps)).reshape(t, n)
+    x = x * w.float().repeat(n // w.shape[0])
+    gf = gate.float()
+    x = x * (F.silu(gf) if act == "silu" else torch.sigmoid(gf)) * out_scale
+    dt = out.dtype if out is not None else (out_dtype or gate.dtype)
+    if out is None:
+        return x.to(dt)
+    out.copy_(x.to(dt))
+    return out
+
+
+def silu_mul(gu: torch.Tensor) -> torch.Tensor:
+    """gu [T, 2F] = [gate | up] -> silu(gate) * up."""
+    f = gu.shape[1] // 2
+    return (F.silu(gu[:, :f].float()) * gu[:, f:].float()).to(gu.dtype)
+
+
+def router_topk(h: torch.Tensor, w: torch.Tensor, top_k: int):
+    """fp32 router logits h . w^T; the top_k largest per token, weights = softmax over the chosen logits only.
+    -> (weights fp32 [T, k], ids int32 [T, k])"""
+    z = h.float() @ w.float().t()
+    val, ids = torch.topk(z, top_k, dim=-1)
+    return torch.softmax(val, -1), ids.to(torch.int32)
+
+
+def softcap(z: torch.Tensor, cap: float) -> torch.Tensor:
+    return (cap * torch.tanh(z.float() / cap)).to(z.dtype)
