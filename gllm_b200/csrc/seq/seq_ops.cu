@@ -14,47 +14,10 @@
 #include <cuda_bf16.h>
 
 #include "common/host_utils.h"
+#include "seq/seq_common.cuh"
 
 namespace {
-
-template <typename T> __device__ __forceinline__ float to_f(T v);
-template <> __device__ __forceinline__ float to_f<float>(float v) { return v; }
-template <> __device__ __forceinline__ float to_f<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
-template <typename T> __device__ __forceinline__ T from_f(float v);
-template <> __device__ __forceinline__ float from_f<float>(float v) { return v; }
-template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
-
-__device__ __forceinline__ float warp_sum(float v) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-  return v;
-}
-__device__ __forceinline__ float warp_max(float v) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
-  return v;
-}
-// sum over a block of NT threads (NT multiple of 32, <= 1024); every thread gets the total
-template <int NT> __device__ __forceinline__ float block_sum(float v, float* scratch) {
-  v = warp_sum(v);
-  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
-  __syncthreads();
-  if (l == 0) scratch[w] = v;
-  __syncthreads();
-  float t = 0.f;
-#pragma unroll
-  for (int i = 0; i < NT / 32; ++i) t += scratch[i];
-  return t;
-}
-// sequence that owns batch row t: largest s with qsl[s] <= t
-__device__ __forceinline__ int find_seq(const int* __restrict__ qsl, int nseq, int t) {
-  int lo = 0, hi = nseq - 1;
-  while (lo < hi) {
-    int mid = (lo + hi + 1) >> 1;
-    if (qsl[mid] <= t) lo = mid; else hi = mid - 1;
-  }
-  return lo;
-}
+using namespace seqk;
 
 // ------------------------------------------------------------------------------------------------
 template <typename T>
@@ -98,10 +61,6 @@ __global__ void __launch_bounds__(256) resid_norm_kernel(float* __restrict__ x, 
   for (int i = threadIdx.x; i < width; i += 256) out[(size_t)t * width + i] = from_f<T>(xr[i] * r * to_f(w_pre[i]));
 }
 
-__device__ __forceinline__ size_t cache_index(int slot, int head, int d, int nheads, int dim, int ps, int slab) {
-  const int page = slot / ps, off = slot - page * ps;
-  return (((size_t)page * nheads + head) * (dim / slab) + d / slab) * ((size_t)ps * slab) + (size_t)off * slab + d % slab;
-}
 
 // one warp per (token, head): heads [0, H) are queries, [H, H + G) keys
 template <typename T>
@@ -134,27 +93,33 @@ __global__ void qk_norm_kv_write_kernel(const T* __restrict__ qk, long ldqk, int
   }
 }
 
-// Sliding-window paged attention with a sink. One warp per (token, head); 4 consecutive tokens of one head per
-// block (their windows overlap, so K/V rows are shared through L1). Scores: one key per lane; P.V: dims across lanes.
+// Masked paged attention with a sink: sliding window and / or chunk mask (position i sees j <= i of its own
+// chunk, floor(i / chunk) == floor(j / chunk)); keys of width D, values of width Dv (their caches have their own
+// slab widths); the result is multiplied by out_scale and written with row stride ldo. One warp per (token, head);
+// 4 consecutive tokens of one head per block (their key ranges overlap, so K/V rows are shared through L1).
+// Scores: one key per lane; P.V: value entries across lanes.
 template <typename T, int MAXR>
 __global__ void __launch_bounds__(128) window_attn_kernel(
     const T* __restrict__ q, const T* __restrict__ kc, const T* __restrict__ vc, const int* __restrict__ block_table,
     int bt_stride, const int* __restrict__ qsl, const int* __restrict__ positions, int ntok, int nseq, float scale,
-    int H, int G, int D, int window, const float* __restrict__ sink, T* __restrict__ out, int ps, int slab) {
-  __shared__ float qs[4][MAXR * 32];
+    int H, int G, int D, int Dv, int window, int chunk, const float* __restrict__ sink, T* __restrict__ out, long ldo,
+    float out_scale, int ps, int slab, int slab_v) {
+  __shared__ float qs[4][256];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x * 4 + warp, h = blockIdx.y;
   if (t >= ntok) return;
   const int s = find_seq(qsl, nseq, t);
   const int i = positions[t];
-  const int lo = window > 0 ? max(0, i - window + 1) : 0;
+  int lo = window > 0 ? max(0, i - window + 1) : 0;
+  if (chunk > 0) lo = max(lo, (i / chunk) * chunk);
   const int g = h / (H / G);
   const T* qrow = q + (size_t)t * H * D + (size_t)h * D;
   for (int d = lane; d < D; d += 32) qs[warp][d] = to_f(qrow[d]);
   __syncwarp();
   const int* bt = block_table + (size_t)s * bt_stride;
   const int nslab = D / slab;
-  const size_t page_stride = (size_t)G * nslab * ps * slab, head_off = (size_t)g * nslab * ps * slab;
+  const size_t page_stride = (size_t)G * D * ps, head_off = (size_t)g * D * ps;
+  const size_t page_stride_v = (size_t)G * Dv * ps, head_off_v = (size_t)g * Dv * ps;
   float m = sink != nullptr ? sink[h] : -INFINITY;
   float l = sink != nullptr ? 1.0f : 0.0f;
   float acc[MAXR];
@@ -163,11 +128,12 @@ __global__ void __launch_bounds__(128) window_attn_kernel(
   for (int j0 = lo; j0 <= i; j0 += 32) {
     const int j = j0 + lane;
     const bool valid = j <= i;
-    size_t base = 0;
+    size_t base_v = 0;
     float sc = -INFINITY;
     if (valid) {
       const int page = bt[j / ps];
-      base = (size_t)page * page_stride + head_off + (size_t)(j % ps) * slab;
+      const size_t base = (size_t)page * page_stride + head_off + (size_t)(j % ps) * slab;
+      base_v = (size_t)page * page_stride_v + head_off_v + (size_t)(j % ps) * slab_v;
       float dot = 0.f;
       for (int c = 0; c < nslab; ++c) {
         const T* kr = kc + base + (size_t)c * ps * slab;
@@ -186,20 +152,20 @@ __global__ void __launch_bounds__(128) window_attn_kernel(
     const int cnt = min(32, i - j0 + 1);
     for (int kk = 0; kk < cnt; ++kk) {
       const float pj = __shfl_sync(0xffffffffu, p, kk);
-      const unsigned long long bj = __shfl_sync(0xffffffffu, (unsigned long long)base, kk);
+      const unsigned long long bj = __shfl_sync(0xffffffffu, (unsigned long long)base_v, kk);
 #pragma unroll
       for (int r = 0; r < MAXR; ++r) {
         const int d = lane + 32 * r;
-        if (d < D) acc[r] = fmaf(pj, to_f(vc[bj + (size_t)(d / slab) * ps * slab + d % slab]), acc[r]);
+        if (d < Dv) acc[r] = fmaf(pj, to_f(vc[bj + (size_t)(d / slab_v) * ps * slab_v + d % slab_v]), acc[r]);
       }
     }
   }
-  T* orow = out + (size_t)t * H * D + (size_t)h * D;
-  const float inv = 1.0f / l;
+  T* orow = out + (size_t)t * ldo + (size_t)h * Dv;
+  const float inv = out_scale / l;
 #pragma unroll
   for (int r = 0; r < MAXR; ++r) {
     const int d = lane + 32 * r;
-    if (d < D) orow[d] = from_f<T>(acc[r] * inv);
+    if (d < Dv) orow[d] = from_f<T>(acc[r] * inv);
   }
 }
 
@@ -394,14 +360,17 @@ int scan_dispatch(int nmax, dim3 grid, cudaStream_t st, const void* xc, const vo
 template <typename T>
 int attn_dispatch(dim3 grid, cudaStream_t st, const void* q, const void* kc, const void* vc, const int* bt,
                   int bt_stride, const int* qsl, const int* pos, int ntok, int nseq, float scale, int H, int G, int D,
-                  int window, const float* sink, void* out, int ps, int slab) {
+                  int Dv, int window, int chunk, const float* sink, void* out, long ldo, float out_scale, int ps,
+                  int slab, int slab_v) {
 #define GLLM_ATTN(R)                                                                                              \
   window_attn_kernel<T, R><<<grid, 128, 0, st>>>((const T*)q, (const T*)kc, (const T*)vc, bt, bt_stride, qsl, pos, \
-                                                 ntok, nseq, scale, H, G, D, window, sink, (T*)out, ps, slab)
-  if (D <= 32) GLLM_ATTN(1);
-  else if (D <= 64) GLLM_ATTN(2);
-  else if (D <= 128) GLLM_ATTN(4);
-  else if (D <= 256) GLLM_ATTN(8);
+                                                 ntok, nseq, scale, H, G, D, Dv, window, chunk, sink, (T*)out, ldo, \
+                                                 out_scale, ps, slab, slab_v)
+  if (D > 256) return 2;
+  if (Dv <= 32) GLLM_ATTN(1);
+  else if (Dv <= 64) GLLM_ATTN(2);
+  else if (Dv <= 128) GLLM_ATTN(4);
+  else if (Dv <= 256) GLLM_ATTN(8);
   else return 2;
 #undef GLLM_ATTN
   return 0;
@@ -460,20 +429,21 @@ GLLM_EXPORT int gllm_seq_qk_norm_kv_write(const void* qk, long ldqk, int ntok, i
 
 GLLM_EXPORT int gllm_seq_window_attention(const void* q, const void* kc, const void* vc, const void* block_table,
                                           int bt_stride, const void* qsl, const void* positions, int ntok, int nseq,
-                                          float scale, int H, int G, int D, int window, const void* sink, void* out,
-                                          int ps, int slab, int is_f32, void* stream) {
+                                          float scale, int H, int G, int D, int Dv, int window, int chunk,
+                                          const void* sink, void* out, long ldo, float out_scale, int ps, int slab,
+                                          int slab_v, int is_f32, void* stream) {
   if (ntok <= 0) return 0;
   cudaStream_t st = (cudaStream_t)stream;
   dim3 grid((ntok + 3) / 4, H);
   int rc;
   if (is_f32)
     rc = attn_dispatch<float>(grid, st, q, kc, vc, (const int*)block_table, bt_stride, (const int*)qsl,
-                              (const int*)positions, ntok, nseq, scale, H, G, D, window, (const float*)sink, out, ps,
-                              slab);
+                              (const int*)positions, ntok, nseq, scale, H, G, D, Dv, window, chunk, (const float*)sink,
+                              out, ldo, out_scale, ps, slab, slab_v);
   else
     rc = attn_dispatch<__nv_bfloat16>(grid, st, q, kc, vc, (const int*)block_table, bt_stride, (const int*)qsl,
-                                      (const int*)positions, ntok, nseq, scale, H, G, D, window, (const float*)sink,
-                                      out, ps, slab);
+                                      (const int*)positions, ntok, nseq, scale, H, G, D, Dv, window, chunk,
+                                      (const float*)sink, out, ldo, out_scale, ps, slab, slab_v);
   if (rc) return rc;
   CUDA_CHECK_RET(cudaGetLastError());
   return 0;

@@ -1,0 +1,500 @@
+// Kernels of the norm-after-sum layer-list decoders (models/hybrid.py, block "postnorm"): the fused residual update
+// x <- rms(alpha x + y) w, per-head q/k RMS norm + rotate-half rotary + paged K / V cache write, the matrix-state
+// linear recurrences (gated delta rule, constant-decay linear attention) with slot-indexed fp32 state, the grouped
+// RMS norm with a gate, SiLU-gated product, the fp32 top-k router with softmax over the chosen logits, plain
+// per-slot expert kernels for shapes / dtypes the grouped tcgen05 GEMM does not take, and the logit cap.
+//
+// Templated on the compute dtype T (bf16 or float); norms, gates, decays, softplus, the router, the recurrences and
+// their state are fp32 in both. Compiled WITHOUT --use_fast_math (build.py). Results of a row never depend on which
+// other rows share the launch: every reduction has a fixed order.
+#include <cuda_bf16.h>
+
+#include "common/host_utils.h"
+#include "seq/seq_common.cuh"
+
+namespace {
+using namespace seqk;
+
+__device__ __forceinline__ float sigmoid_f(float v) { return 1.0f / (1.0f + expf(-v)); }
+__device__ __forceinline__ float silu_f(float v) { return v / (1.0f + expf(-v)); }
+
+// x <- rms(alpha * x + y) * w (fp32 stream, in place); out = the same row in the compute dtype (optional)
+template <typename T>
+__global__ void __launch_bounds__(256) postnorm_kernel(float* __restrict__ x, const T* __restrict__ y, long ldy,
+                                                       const T* __restrict__ w, T* __restrict__ out, int width,
+                                                       float alpha, float eps) {
+  __shared__ float scratch[8];
+  const int t = blockIdx.x;
+  float* xr = x + (size_t)t * width;
+  const T* yr = y + (size_t)t * ldy;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < width; i += 256) {
+    const float v = fmaf(alpha, xr[i], to_f(yr[i]));
+    ss += v * v;
+  }
+  ss = block_sum<256>(ss, scratch);
+  const float r = 1.0f / sqrtf(ss / (float)width + eps);
+  for (int i = threadIdx.x; i < width; i += 256) {
+    const float v = fmaf(alpha, xr[i], to_f(yr[i])) * r * to_f(w[i]);
+    xr[i] = v;
+    if (out != nullptr) out[(size_t)t * width + i] = from_f<T>(v);
+  }
+}
+
+// One warp per (token, head): heads [0, H) queries, [H, H + G) keys, [H + G, H + 2G) values (copied to the V cache).
+// q / k: RMS norm over D with a shared weight, then entries i and i + rot/2 (i < rot/2) turn by pos * base^(-2i/rot).
+// The angle is formed in fp64 (no table, no maximum position), the rotation itself in fp32.
+template <typename T>
+__global__ void qk_norm_rope_kv_write_kernel(const T* __restrict__ qkv, long ld, int H, int G, int D, int Dv,
+                                             const T* __restrict__ qn, const T* __restrict__ kn, float eps,
+                                             const int* __restrict__ positions, int rot, double log2_base,
+                                             T* __restrict__ q_out, T* __restrict__ kc, T* __restrict__ vc,
+                                             const int* __restrict__ slots, int ps, int slab, int slab_v) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int head = blockIdx.y * 4 + warp, t = blockIdx.x;
+  if (head >= H + 2 * G) return;
+  const int slot = slots[t];
+  if (head >= H + G) {
+    if (slot < 0) return;
+    const int g = head - H - G;
+    const T* src = qkv + (size_t)t * ld + (size_t)(H + G) * D + (size_t)g * Dv;
+    for (int d = lane; d < Dv; d += 32) vc[cache_index(slot, g, d, G, Dv, ps, slab_v)] = src[d];
+    return;
+  }
+  const T* src = qkv + (size_t)t * ld + (size_t)head * D;
+  float ss = 0.f;
+  for (int d = lane; d < D; d += 32) { const float v = to_f(src[d]); ss += v * v; }
+  ss = warp_sum(ss);
+  const T* w = head < H ? qn : kn;
+  const float r = w != nullptr ? 1.0f / sqrtf(ss / (float)D + eps) : 1.0f;
+  const int half = rot / 2;
+  const double pos = (double)positions[t];
+  if (head >= H && slot < 0) return;
+  for (int d = lane; d < D; d += 32) {
+    float v = to_f(src[d]) * r * (w != nullptr ? to_f(w[d]) : 1.0f);
+    if (d < rot) {
+      const int i = d < half ? d : d - half, pd = d < half ? d + half : d - half;
+      const float other = to_f(src[pd]) * r * (w != nullptr ? to_f(w[pd]) : 1.0f);
+      double sn, cs;
+      sincos(pos * exp2(-(2.0 * (double)i / (double)rot) * log2_base), &sn, &cs);
+      const float c = (float)cs, s = (float)sn;
+      v = d < half ? v * c - other * s : v * c + other * s;
+    }
+    if (head < H) q_out[(size_t)t * H * D + (size_t)head * D + d] = from_f<T>(v);
+    else kc[cache_index(slot, head - H, d, G, D, ps, slab)] = from_f<T>(v);
+  }
+}
+
+// Matrix-state recurrence, one block per (sequence, head, 32 value columns). A value column's D state entries are
+// split over 4 adjacent lanes (entry d = part + 4 j), NS per lane in registers; per token
+//     S <- g S;  u = delta ? beta (v - S^T k) : v;  S <- S + k u^T;  o = S^T q
+// costs two register passes and two 4-lane shuffles. q / k rows and the per-token g, beta of TCH tokens are staged
+// in shared memory by the whole block (SiLU, unit length and the q scale applied there).
+template <typename T, int NS>
+__global__ void __launch_bounds__(128) linear_state_kernel(
+    const T* __restrict__ q, long ldq, const T* __restrict__ k, long ldk, const T* __restrict__ v, long ldv,
+    const T* __restrict__ beta, long ldb, const T* __restrict__ a, long lda, const float* __restrict__ neg_a,
+    const float* __restrict__ dt_bias, const float* __restrict__ decay, float* __restrict__ state,
+    const int* __restrict__ rec_slots, const int* __restrict__ seq_lens, const int* __restrict__ qsl, int H, int G,
+    int D, int V, int silu_in, int unit_qk, float q_scale, int delta, float* __restrict__ out) {
+  constexpr int TCH = 8;
+  extern __shared__ float sm[];
+  float* sq = sm;                      // [TCH][2][D]: q row, k row
+  float* sg = sm + TCH * 2 * D;        // [TCH][2]: g, beta
+  const int s = blockIdx.x, h = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int vl = threadIdx.x >> 2, part = threadIdx.x & 3;
+  const int vcol = blockIdx.z * 32 + vl;
+  const bool active = vcol < V;
+  const int vc = active ? vcol : V - 1;          // idle lanes mirror the last column (loads only)
+  const int q0 = qsl[s], q1 = qsl[s + 1];
+  if (q1 <= q0) return;                          // uniform over the block
+  const bool carried = state != nullptr && (seq_lens[s] - (q1 - q0)) > 0;
+  float* st = state != nullptr ? state + ((size_t)rec_slots[s] * H + h) * (size_t)D * V : nullptr;
+  float S[NS];
+#pragma unroll
+  for (int j = 0; j < NS; ++j) {
+    const int d = part + 4 * j;
+    S[j] = (carried && d < D) ? st[(size_t)d * V + vc] : 0.f;
+  }
+  const int kvh = h / (H / G);
+  for (int t0 = q0; t0 < q1; t0 += TCH) {
+    const int nt = min(TCH, q1 - t0);
+    __syncthreads();                             // the previous chunk's rows are consumed
+    for (int idx = threadIdx.x; idx < nt * 2 * D; idx += 128) {
+      const int kk = idx / (2 * D), r = idx - kk * 2 * D;
+      float f = r < D ? to_f(q[(size_t)(t0 + kk) * ldq + (size_t)kvh * D + r])
+                      : to_f(k[(size_t)(t0 + kk) * ldk + (size_t)kvh * D + r - D]);
+      if (silu_in) f = silu_f(f);
+      sq[idx] = f;
+    }
+    if (threadIdx.x < nt) {
+      float g, b = 1.0f;
+      if (decay != nullptr) {
+        g = decay[h];
+      } else {
+        const float z = to_f(a[(size_t)(t0 + threadIdx.x) * lda + h]) + dt_bias[h];
+        g = expf(neg_a[h] * (z > 20.0f ? z : log1pf(expf(z))));
+      }
+      if (delta) b = sigmoid_f(to_f(beta[(size_t)(t0 + threadIdx.x) * ldb + h]));
+      sg[threadIdx.x * 2] = g;
+      sg[threadIdx.x * 2 + 1] = b;
+    }
+    __syncthreads();
+    if (unit_qk || q_scale != 1.0f) {
+      for (int row = warp; row < 2 * nt; row += 4) {      // row = token * 2 + (0: q, 1: k)
+        float* ptr = sq + (size_t)row * D;
+        float sc = (row & 1) ? 1.0f : q_scale;
+        if (unit_qk) {
+          float ss = 0.f;
+          for (int d = lane; d < D; d += 32) ss += ptr[d] * ptr[d];
+          sc /= sqrtf(warp_sum(ss) + 1e-6f);
+        }
+        for (int d = lane; d < D; d += 32) ptr[d] *= sc;
+      }
+      __syncthreads();
+    }
+    float vv[TCH];
+#pragma unroll
+    for (int kk = 0; kk < TCH; ++kk) {
+      if (kk < nt) {
+        const float f = to_f(v[(size_t)(t0 + kk) * ldv + (size_t)h * V + vc]);
+        vv[kk] = silu_in ? silu_f(f) : f;
+      }
+    }
+#pragma unroll
+    for (int kk = 0; kk < TCH; ++kk) {
+      if (kk < nt) {
+        const float* qq = sq + (size_t)kk * 2 * D;
+        const float* kr = qq + D;
+        const float g = sg[kk * 2], b = sg[kk * 2 + 1];
+        float u = vv[kk];
+        if (delta) {
+          float dot = 0.f;
+#pragma unroll
+          for (int j = 0; j < NS; ++j) {
+            const int d = part + 4 * j;
+            if (d < D) dot = fmaf(S[j], kr[d], dot);
+          }
+          dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+          dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+          u = b * (u - g * dot);
+        }
+        float o = 0.f;
+#pragma unroll
+        for (int j = 0; j < NS; ++j) {
+          const int d = part + 4 * j;
+          if (d < D) {
+            S[j] = fmaf(kr[d], u, g * S[j]);
+            o = fmaf(S[j], qq[d], o);
+          }
+        }
+        o += __shfl_xor_sync(0xffffffffu, o, 1);
+        o += __shfl_xor_sync(0xffffffffu, o, 2);
+        if (active && part == 0) out[(size_t)(t0 + kk) * H * V + (size_t)h * V + vcol] = o;
+      }
+    }
+  }
+  if (st != nullptr && active) {
+#pragma unroll
+    for (int j = 0; j < NS; ++j) {
+      const int d = part + 4 * j;
+      if (d < D) st[(size_t)d * V + vcol] = S[j];
+    }
+  }
+}
+
+// one warp per (token, group): out = rms_group(o) * w[col % wlen] * act(gate) * out_scale
+template <typename T>
+__global__ void gated_group_norm_kernel(const float* __restrict__ o, int n, const T* __restrict__ gate, long ldg,
+                                        const T* __restrict__ w, int wlen, int group, float eps, int act,
+                                        float out_scale, T* __restrict__ out, long ldo, int ntok) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int ngroups = n / group;
+  const long gw = (long)blockIdx.x * 4 + warp;
+  if (gw >= (long)ntok * ngroups) return;
+  const int t = (int)(gw / ngroups), gi = (int)(gw % ngroups);
+  const float* src = o + (size_t)t * n + (size_t)gi * group;
+  float ss = 0.f;
+  for (int d = lane; d < group; d += 32) ss += src[d] * src[d];
+  ss = warp_sum(ss);
+  const float r = 1.0f / sqrtf(ss / (float)group + eps);
+  for (int d = lane; d < group; d += 32) {
+    const int col = gi * group + d;
+    const float gt = to_f(gate[(size_t)t * ldg + col]);
+    const float ga = act ? sigmoid_f(gt) : silu_f(gt);
+    out[(size_t)t * ldo + col] = from_f<T>(src[d] * r * to_f(w[col % wlen]) * ga * out_scale);
+  }
+}
+
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ gu, long ld, int F, T* __restrict__ out, size_t total) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const size_t t = i / F, f = i - t * F;
+  out[i] = from_f<T>(silu_f(to_f(gu[t * ld + f])) * to_f(gu[t * ld + F + f]));
+}
+
+// One block per token: fp32 logits (one expert per warp at a time, lanes over the width, fixed order), then warp 0
+// picks the top_k largest (ties: the lower index) and softmaxes over the chosen logits only.
+template <typename T>
+__global__ void __launch_bounds__(128) router_topk_kernel(const T* __restrict__ h, long ldh, const T* __restrict__ w,
+                                                          int width, int E, int top_k, float* __restrict__ wout,
+                                                          int* __restrict__ ids) {
+  extern __shared__ float logit[];     // [E] then chosen values [top_k]
+  float* chosen = logit + E;
+  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const T* hr = h + (size_t)t * ldh;
+  for (int e = warp; e < E; e += 4) {
+    const T* wr = w + (size_t)e * width;
+    float acc = 0.f;
+    for (int i = lane; i < width; i += 32) acc = fmaf(to_f(hr[i]), to_f(wr[i]), acc);
+    acc = warp_sum(acc);
+    if (lane == 0) logit[e] = acc;
+  }
+  __syncthreads();
+  if (warp != 0) return;
+  for (int kk = 0; kk < top_k; ++kk) {
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int e = lane; e < E; e += 32) {
+      const float v = logit[e];
+      if (v > best) { best = v; bi = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    if (bi >= E) bi = kk < E ? kk : 0;           // only when every remaining logit is -inf / NaN
+    if (lane == 0) {
+      chosen[kk] = best;
+      ids[(size_t)t * top_k + kk] = bi;
+      logit[bi] = -INFINITY;
+    }
+    __syncwarp();
+  }
+  if (lane == 0) {
+    const float m = chosen[0];                   // the first pick is the largest
+    float den = 0.f;
+    for (int kk = 0; kk < top_k; ++kk) { chosen[kk] = expf(chosen[kk] - m); den += chosen[kk]; }
+    for (int kk = 0; kk < top_k; ++kk) wout[(size_t)t * top_k + kk] = chosen[kk] / den;
+  }
+}
+
+// plain experts, first half: act[slot, f] = silu(gate_e[f] . h) * (up_e[f] . h); one warp per (slot, f)
+template <typename T>
+__global__ void __launch_bounds__(128) moe_gate_up_kernel(const T* __restrict__ h, long ldh,
+                                                          const T* __restrict__ w13, const int* __restrict__ ids,
+                                                          int top_k, int width, int F, T* __restrict__ act) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int slot = blockIdx.x, f = blockIdx.y * 4 + warp;
+  if (f >= F) return;
+  const int e = ids[slot];
+  const T* hr = h + (size_t)(slot / top_k) * ldh;
+  const T* gr = w13 + ((size_t)e * 2 * F + f) * width;
+  const T* ur = gr + (size_t)F * width;
+  float ga = 0.f, ua = 0.f;
+  for (int i = lane; i < width; i += 32) {
+    const float x = to_f(hr[i]);
+    ga = fmaf(x, to_f(gr[i]), ga);
+    ua = fmaf(x, to_f(ur[i]), ua);
+  }
+  ga = warp_sum(ga);
+  ua = warp_sum(ua);
+  if (lane == 0) act[(size_t)slot * F + f] = from_f<T>(silu_f(ga) * ua);
+}
+
+// plain experts, second half: out[t, c] = sum_k weight[t, k] * (down_e[c] . act[t * top_k + k]); one warp per (t, c)
+template <typename T>
+__global__ void __launch_bounds__(128) moe_down_kernel(const T* __restrict__ act, const T* __restrict__ w2,
+                                                       const int* __restrict__ ids, const float* __restrict__ wts,
+                                                       int top_k, int width, int F, T* __restrict__ out) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x, c = blockIdx.y * 4 + warp;
+  if (c >= width) return;
+  float total = 0.f;
+  for (int kk = 0; kk < top_k; ++kk) {
+    const int e = ids[(size_t)t * top_k + kk];
+    const T* ar = act + ((size_t)t * top_k + kk) * F;
+    const T* dr = w2 + ((size_t)e * width + c) * F;
+    float acc = 0.f;
+    for (int i = lane; i < F; i += 32) acc = fmaf(to_f(ar[i]), to_f(dr[i]), acc);
+    total = fmaf(wts[(size_t)t * top_k + kk], warp_sum(acc), total);
+  }
+  if (lane == 0) out[(size_t)t * width + c] = from_f<T>(total);
+}
+
+template <typename T>
+__global__ void softcap_kernel(T* __restrict__ z, long ld, int n, float cap, size_t total) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const size_t t = i / n, c = i - t * n;
+  z[t * ld + c] = from_f<T>(cap * tanhf(to_f(z[t * ld + c]) / cap));
+}
+
+template <typename T>
+int state_dispatch(dim3 grid, size_t smem, cudaStream_t st, const void* q, long ldq, const void* k, long ldk,
+                   const void* v, long ldv, const void* beta, long ldb, const void* a, long lda, const float* neg_a,
+                   const float* dt_bias, const float* decay, float* state, const int* rec_slots, const int* seq_lens,
+                   const int* qsl, int H, int G, int D, int V, int silu_in, int unit_qk, float q_scale, int delta,
+                   float* out) {
+#define GLLM_STATE(NS)                                                                                              \
+  linear_state_kernel<T, NS><<<grid, 128, smem, st>>>((const T*)q, ldq, (const T*)k, ldk, (const T*)v, ldv,         \
+                                                      (const T*)beta, ldb, (const T*)a, lda, neg_a, dt_bias, decay, \
+                                                      state, rec_slots, seq_lens, qsl, H, G, D, V, silu_in, unit_qk, \
+                                                      q_scale, delta, out)
+  if (D <= 16) GLLM_STATE(4);
+  else if (D <= 32) GLLM_STATE(8);
+  else if (D <= 64) GLLM_STATE(16);
+  else if (D <= 128) GLLM_STATE(32);
+  else if (D <= 256) GLLM_STATE(64);
+  else return 2;
+#undef GLLM_STATE
+  return 0;
+}
+
+}  // namespace
+
+#define GLLM_BY_DTYPE(is_f32, CALL_BF16, CALL_F32) \
+  do { if (is_f32) { CALL_F32; } else { CALL_BF16; } } while (0)
+typedef __nv_bfloat16 bf16_t;
+
+GLLM_EXPORT int gllm_seq_postnorm(void* x, const void* y, long ldy, const void* w, void* out, int ntok, int width,
+                                  float alpha, float eps, int is_f32, void* stream) {
+  if (ntok <= 0) return 0;
+  cudaStream_t st = (cudaStream_t)stream;
+  GLLM_BY_DTYPE(is_f32,
+                (postnorm_kernel<bf16_t><<<ntok, 256, 0, st>>>((float*)x, (const bf16_t*)y, ldy, (const bf16_t*)w,
+                                                               (bf16_t*)out, width, alpha, eps)),
+                (postnorm_kernel<float><<<ntok, 256, 0, st>>>((float*)x, (const float*)y, ldy, (const float*)w,
+                                                              (float*)out, width, alpha, eps)));
+  CUDA_CHECK_RET(cudaGetLastError());
+  return 0;
+}
+
+GLLM_EXPORT int gllm_seq_qk_norm_rope_kv_write(const void* qkv, long ld, int ntok, int H, int G, int D, int Dv,
+                                               const void* qn, const void* kn, float eps, const void* positions,
+                                               int rot, double log2_base, void* q_out, void* kc, void* vc,
+                                               const void* slots, int ps, int slab, int slab_v, int is_f32,
+                                               void* stream) {
+  if (ntok <= 0) return 0;
+  cudaStream_t st = (cudaStream_t)stream;
+  dim3 grid(ntok, (H + 2 * G + 3) / 4);
+  GLLM_BY_DTYPE(is_f32,
+                (qk_norm_rope_kv_write_kernel<bf16_t><<<grid, 128, 0, st>>>(
+                    (const bf16_t*)qkv, ld, H, G, D, Dv, (const bf16_t*)qn, (const bf16_t*)kn, eps,
+                    (const int*)positions, rot, log2_base, (bf16_t*)q_out, (bf16_t*)kc, (bf16_t*)vc,
+                    (const int*)slots, ps, slab, slab_v)),
+                (qk_norm_rope_kv_write_kernel<float><<<grid, 128, 0, st>>>(
+                    (const float*)qkv, ld, H, G, D, Dv, (const float*)qn, (const float*)kn, eps,
+                    (const int*)positions, rot, log2_base, (float*)q_out, (float*)kc, (float*)vc, (const int*)slots,
+                    ps, slab, slab_v)));
+  CUDA_CHECK_RET(cudaGetLastError());
+  return 0;
+}
+
+GLLM_EXPORT int gllm_seq_linear_state(const void* q, long ldq, const void* k, long ldk, const void* v, long ldv,
+                                      const void* beta, long ldb, const void* a, long lda, const void* neg_a,
+                                      const void* dt_bias, const void* decay, void* state, const void* rec_slots,
+                                      const void* seq_lens, const void* qsl, int nseq, int H, int G, int D, int V,
+                                      int silu_in, int unit_qk, float q_scale, int delta, void* out, int is_f32,
+                                      void* stream) {
+  if (nseq <= 0) return 0;
+  cudaStream_t st = (cudaStream_t)stream;
+  dim3 grid(nseq, H, (V + 31) / 32);
+  const size_t smem = (size_t)(8 * 2 * D + 16) * sizeof(float);
+  int rc;
+  if (is_f32)
+    rc = state_dispatch<float>(grid, smem, st, q, ldq, k, ldk, v, ldv, beta, ldb, a, lda, (const float*)neg_a,
+                               (const float*)dt_bias, (const float*)decay, (float*)state, (const int*)rec_slots,
+                               (const int*)seq_lens, (const int*)qsl, H, G, D, V, silu_in, unit_qk, q_scale, delta,
+                               (float*)out);
+  else
+    rc = state_dispatch<bf16_t>(grid, smem, st, q, ldq, k, ldk, v, ldv, beta, ldb, a, lda, (const float*)neg_a,
+                                (const float*)dt_bias, (const float*)decay, (float*)state, (const int*)rec_slots,
+                                (const int*)seq_lens, (const int*)qsl, H, G, D, V, silu_in, unit_qk, q_scale, delta,
+                                (float*)out);
+  if (rc) return rc;
+  CUDA_CHECK_RET(cudaGetLastError());
+  return 0;
+}
+
+GLLM_EXPORT int gllm_seq_gated_group_norm(const void* o, int n, const void* gate, long ldg, const void* w, int wlen,
+                                          int group, float eps, int act, float out_scale, void* out, long ldo,
+                                          int ntok, int is_f32, void* stream) {
+  if (ntok <= 0 || n <= 0) return 0;
+  if (group <= 0 || n % group != 0) return 2;
+  cudaStream_t st = (cudaStream_t)stream;
+  const long warps = (long)ntok * (n / group);
+  const unsigned blocks = (unsigned)((warps + 3) / 4);
+  GLLM_BY_DTYPE(is_f32,
+                (gated_group_norm_kernel<bf16_t><<<blocks, 128, 0, st>>>((const float*)o, n, (const bf16_t*)gate, ldg,
+                                                                         (const bf16_t*)w, wlen, group, eps, act,
+                                                                         out_scale, (bf16_t*)out, ldo, ntok)),
+                (gated_group_norm_kernel<float><<<blocks, 128, 0, st>>>((const float*)o, n, (const float*)gate, ldg,
+                                                                        (const float*)w, wlen, group, eps, act,
+                                                                        out_scale, (float*)out, ldo, ntok)));
+  CUDA_CHECK_RET(cudaGetLastError());
+  return 0;
+}
+
+GLLM_EXPORT int gllm_seq_silu_mul(const void* gu, long ld, int ntok, int F, void* out, int is_f32, void* stream) {
+  if (ntok <= 0 || F <= 0) return 0;
+  cudaStream_t st = (cudaStream_t)stream;
+  const size_t total = (size_t)ntok * F;
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  GLLM_BY_DTYPE(is_f32,
+                (silu_mul_kernel<bf16_t><<<blocks, 256, 0, st>>>((const bf16_t*)gu, ld, F, (bf16_t*)out, total)),
+                (silu_mul_kernel<float><<<blocks, 256, 0, st>>>((const float*)gu, ld, F, (float*)out, total)));
+  CUDA_CHECK_RET(cudaGetLastError());
+  return 0;
+}
+
+GLLM_EXPORT int gllm_seq_router_topk(const void* h, long ldh, const void* w, int ntok, int width, int E, int top_k,
+                                     void* wout, void* ids, int is_f32, void* stream) {
+  if (ntok <= 0) return 0;
+  if (top_k > E || E > 8192) return 2;
+  cudaStream_t st = (cudaStream_t)stream;
+  const size_t smem = (size_t)(E + top_k) * sizeof(float);
+  GLLM_BY_DTYPE(is_f32,
+                (router_topk_kernel<bf16_t><<<ntok, 128, smem, st>>>((const bf16_t*)h, ldh, (const bf16_t*)w, width, E,
+                                                                     top_k, (float*)wout, (int*)ids)),
+                (router_topk_kernel<float><<<ntok, 128, smem, st>>>((const float*)h, ldh, (const float*)w, width, E,
+                                                                    top_k, (float*)wout, (int*)ids)));
+  CUDA_CHECK_RET(cudaGetLastError());
+  return 0;
+}
+
+GLLM_EXPORT int gllm_seq_routed_experts(const void* h, long ldh, const void* w13, const void* w2, const void* ids,
+                                        const void* wts, int ntok, int top_k, int width, int F, void* act, void* out,
+                                        int is_f32, void* stream) {
+  if (ntok <= 0) return 0;
+  cudaStream_t st = (cudaStream_t)stream;
+  dim3 g1(ntok * top_k, (F + 3) / 4), g2(ntok, (width + 3) / 4);
+  if (is_f32) {
+    moe_gate_up_kernel<float><<<g1, 128, 0, st>>>((const float*)h, ldh, (const float*)w13, (const int*)ids, top_k,
+                                                  width, F, (float*)act);
+    moe_down_kernel<float><<<g2, 128, 0, st>>>((const float*)act, (const float*)w2, (const int*)ids,
+                                               (const float*)wts, top_k, width, F, (float*)out);
+  } else {
+    moe_gate_up_kernel<bf16_t><<<g1, 128, 0, st>>>((const bf16_t*)h, ldh, (const bf16_t*)w13, (const int*)ids, top_k,
+                                                   width, F, (bf16_t*)act);
+    moe_down_kernel<bf16_t><<<g2, 128, 0, st>>>((const bf16_t*)act, (const bf16_t*)w2, (const int*)ids,
+                                                (const float*)wts, top_k, width, F, (bf16_t*)out);
+  }
+  CUDA_CHECK_RET(cudaGetLastError());
+  return 0;
+}
+
+GLLM_EXPORT int gllm_seq_softcap(void* z, long ld, int ntok, int n, float cap, int is_f32, void* stream) {
+  if (ntok <= 0 || n <= 0) return 0;
+  cudaStream_t st = (cudaStream_t)stream;
+  const size_t total = (size_t)ntok * n;
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  GLLM_BY_DTYPE(is_f32, (softcap_kernel<bf16_t><<<blocks, 256, 0, st>>>((bf16_t*)z, ld, n, cap, total)),
+                (softcap_kernel<float><<<blocks, 256, 0, st>>>((float*)z, ld, n, cap, total)));
+  CUDA_CHECK_RET(cudaGetLastError());
+  return 0;
+}

@@ -28,7 +28,17 @@ def _L():
             "gllm_seq_embed_scale": [P, P, P, I, I, I, F, I, P],
             "gllm_seq_resid_norm": [P, P, G, P, P, P, P, I, I, F, I, P],
             "gllm_seq_qk_norm_kv_write": [P, G, I, I, I, I, P, P, F, P, P, P, P, I, I, I, P],
-            "gllm_seq_window_attention": [P, P, P, P, I, P, P, I, I, F, I, I, I, I, P, P, I, I, I, P],
+            "gllm_seq_window_attention": [P, P, P, P, I, P, P, I, I, F, I, I, I, I, I, I, P, P, G, F, I, I, I, I, P],
+            "gllm_seq_postnorm": [P, P, G, P, P, I, I, F, F, I, P],
+            "gllm_seq_qk_norm_rope_kv_write": [P, G, I, I, I, I, I, P, P, F, P, I, ctypes.c_double, P, P, P, P, I, I, I,
+                                               I, P],
+            "gllm_seq_linear_state": [P, G, P, G, P, G, P, G, P, G, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, P,
+                                      I, P],
+            "gllm_seq_gated_group_norm": [P, I, P, G, P, I, I, F, I, F, P, G, I, I, P],
+            "gllm_seq_silu_mul": [P, G, I, I, P, I, P],
+            "gllm_seq_router_topk": [P, G, P, I, I, I, I, P, P, I, P],
+            "gllm_seq_routed_experts": [P, G, P, P, P, P, I, I, I, I, P, P, I, P],
+            "gllm_seq_softcap": [P, G, I, I, F, I, P],
             "gllm_seq_conv_silu": [P, G, I, I, I, P, P, I, P, P, P, P, P, I, P],
             "gllm_seq_selective_scan": [P, P, P, G, P, G, P, P, P, P, P, P, P, I, I, I, I, P, I, I, P],
             "gllm_seq_relu2": [P, P, G, I, P],
@@ -112,17 +122,22 @@ def qk_norm_kv_write(qk, num_heads, num_kv_heads, dim, q_norm_w, k_norm_w, eps, 
 
 def window_attention(q, k_cache, v_cache, block_table, seq_lens, query_start_loc, positions, scale, num_q_heads,
                      head_dim, window, sink, num_decode_seqs: int = 0, max_q_len: Optional[int] = None,
-                     simt: bool = False):
+                     simt: bool = False, chunk: Optional[int] = None, v_dim: Optional[int] = None,
+                     out_scale: float = 1.0, out: Optional[torch.Tensor] = None):
     """Sliding-window (None / 0 = full causal) paged attention with an optional per-head softmax sink. bf16 with
     head_dim 64 / 128 / 256 and pages of 8..64 tokens runs on the tensor-core paged-attention kernels
     (csrc/attn/paged_attention.cu: the first `num_decode_seqs` sequences, one token each, on the decode kernel, the
     rest on the prefill kernel); everything else (fp32, other head sizes or page sizes) on the plain kernel."""
     t = q.shape[0]
-    out = torch.empty_like(q)
+    v_dim = head_dim if v_dim is None else v_dim
+    if out is None:
+        out = torch.empty(t, num_q_heads * v_dim, dtype=q.dtype, device=q.device)
     ps, slab = k_cache.shape[3], k_cache.shape[4]
     assert q.is_contiguous() and block_table.stride(1) == 1 and positions.dim() == 1
+    assert out.stride(1) == 1 and out.dtype == q.dtype and v_cache.shape[3] == ps
     nseq = seq_lens.shape[0]
-    if not simt and q.dtype == torch.bfloat16 and head_dim in (64, 128, 256) and slab == 64 and ps >= 8 and \
+    plain_only = bool(chunk) or v_dim != head_dim or out_scale != 1.0 or out.stride(0) != num_q_heads * v_dim
+    if not simt and not plain_only and q.dtype == torch.bfloat16 and head_dim in (64, 128, 256) and slab == 64 and ps >= 8 and \
             64 % ps == 0 and max_q_len is not None:
         L, st = _L(), stream_ptr()
         pages, hkv = k_cache.shape[0], k_cache.shape[1]
@@ -142,8 +157,9 @@ def window_attention(q, k_cache, v_cache, block_table, seq_lens, query_start_loc
         return out
     check(_L().gllm_seq_window_attention(_p(q), _p(k_cache), _p(v_cache), _p(block_table), block_table.stride(0),
                                          _p(query_start_loc), _p(positions), t, seq_lens.shape[0], float(scale),
-                                         num_q_heads, k_cache.shape[1], head_dim, int(window or 0), _p(sink), _p(out),
-                                         ps, slab, _f32(q), stream_ptr()), "seq_window_attention")
+                                         num_q_heads, k_cache.shape[1], head_dim, v_dim, int(window or 0),
+                                         int(chunk or 0), _p(sink), _p(out), out.stride(0), float(out_scale), ps, slab,
+                                         v_cache.shape[4], _f32(q), stream_ptr()), "seq_window_attention")
     sm100._count()
     return out
 
@@ -181,3 +197,100 @@ def relu2(x):
     check(_L().gllm_seq_relu2(_p(x), _p(out), x.numel(), _f32(x), stream_ptr()), "seq_relu2")
     sm100._count()
     return out
+
+
+def postnorm(x, y, alpha, w, eps, out_dtype):
+    assert x.dtype == torch.float32 and x.is_contiguous() and y.stride(1) == 1 and y.dtype == w.dtype
+    t, width = x.shape
+    out = None if out_dtype == torch.float32 else torch.empty(t, width, dtype=out_dtype, device=x.device)
+    check(_L().gllm_seq_postnorm(_p(x), _p(y), y.stride(0), _p(w), _p(out), t, width, float(alpha), float(eps),
+                                 _f32(y), stream_ptr()), "seq_postnorm")
+    sm100._count()
+    return x if out is None else out
+
+
+def qk_norm_rope_kv_write(qkv, num_heads, num_kv_heads, dim, v_dim, q_norm_w, k_norm_w, eps, positions, rot_dims,
+                          rot_base, k_cache, v_cache, slots):
+    import math
+    t = qkv.shape[0]
+    assert qkv.stride(1) == 1 and k_cache.dtype == qkv.dtype and positions.dim() == 1
+    q = torch.empty(t, num_heads * dim, dtype=qkv.dtype, device=qkv.device)
+    ps = k_cache.shape[3]
+    check(_L().gllm_seq_qk_norm_rope_kv_write(_p(qkv), qkv.stride(0), t, num_heads, num_kv_heads, dim, v_dim,
+                                              _p(q_norm_w), _p(k_norm_w), float(eps), _p(positions), int(rot_dims),
+                                              math.log2(rot_base) if rot_dims > 0 else 0.0, _p(q), _p(k_cache),
+                                              _p(v_cache), _p(slots), ps, k_cache.shape[4], v_cache.shape[4],
+                                              _f32(qkv), stream_ptr()), "seq_qk_norm_rope_kv_write")
+    sm100._count()
+    return q
+
+
+def linear_state_scan(q, k, v, beta, a, neg_a, dt_bias, decay, state, rec_slots, seq_lens, query_start_loc, heads,
+                      qk_heads, dim, v_dim, silu_in, unit_qk, q_scale, delta):
+    t = q.shape[0]
+    for x in (q, k, v, beta, a):
+        assert x is None or (x.stride(1) == 1 and x.dtype == q.dtype)
+    assert state is None or (state.dtype == torch.float32 and state.is_contiguous())
+    assert (decay is None) != (a is None) and (not delta or beta is not None)
+    out = torch.empty(t, heads * v_dim, dtype=torch.float32, device=q.device)
+    ld = lambda x: x.stride(0) if x is not None else 0   # noqa: E731
+    check(_L().gllm_seq_linear_state(_p(q), q.stride(0), _p(k), k.stride(0), _p(v), v.stride(0), _p(beta), ld(beta),
+                                     _p(a), ld(a), _p(neg_a), _p(dt_bias), _p(decay), _p(state), _p(rec_slots),
+                                     _p(seq_lens), _p(query_start_loc), seq_lens.shape[0], heads, qk_heads, dim, v_dim,
+                                     int(silu_in), int(unit_qk), float(q_scale), int(delta), _p(out), _f32(q),
+                                     stream_ptr()), "seq_linear_state")
+    sm100._count()
+    return out
+
+
+def gated_group_norm(o, gate, w, group, eps, act, out_scale=1.0, out=None, out_dtype=None):
+    t, n = o.shape
+    assert o.dtype == torch.float32 and o.is_contiguous() and gate.stride(1) == 1 and gate.dtype == w.dtype
+    if out is None:
+        out = torch.empty(t, n, dtype=out_dtype or gate.dtype, device=o.device)
+    assert out.stride(1) == 1 and out.dtype == gate.dtype
+    check(_L().gllm_seq_gated_group_norm(_p(o), n, _p(gate), gate.stride(0), _p(w), w.shape[0], int(group), float(eps),
+                                         1 if act == "sigmoid" else 0, float(out_scale), _p(out), out.stride(0), t,
+                                         _f32(gate), stream_ptr()), "seq_gated_group_norm")
+    sm100._count()
+    return out
+
+
+def silu_mul(gu):
+    t, f = gu.shape[0], gu.shape[1] // 2
+    assert gu.stride(1) == 1
+    out = torch.empty(t, f, dtype=gu.dtype, device=gu.device)
+    check(_L().gllm_seq_silu_mul(_p(gu), gu.stride(0), t, f, _p(out), _f32(gu), stream_ptr()), "seq_silu_mul")
+    sm100._count()
+    return out
+
+
+def router_topk(h, w, top_k):
+    t, width = h.shape
+    assert h.stride(1) == 1 and w.is_contiguous() and h.dtype == w.dtype
+    wout = torch.empty(t, top_k, dtype=torch.float32, device=h.device)
+    ids = torch.empty(t, top_k, dtype=torch.int32, device=h.device)
+    check(_L().gllm_seq_router_topk(_p(h), h.stride(0), _p(w), t, width, w.shape[0], top_k, _p(wout), _p(ids),
+                                    _f32(h), stream_ptr()), "seq_router_topk")
+    sm100._count()
+    return wout, ids
+
+
+def routed_experts(h, w13, w2, weights, ids):
+    t, width = h.shape
+    f, k = w13.shape[1] // 2, ids.shape[1]
+    assert h.stride(1) == 1 and w13.is_contiguous() and w2.is_contiguous() and weights.is_contiguous()
+    act = torch.empty(t * k, f, dtype=h.dtype, device=h.device)
+    out = torch.empty(t, width, dtype=h.dtype, device=h.device)
+    check(_L().gllm_seq_routed_experts(_p(h), h.stride(0), _p(w13), _p(w2), _p(ids), _p(weights), t, k, width, f,
+                                       _p(act), _p(out), _f32(h), stream_ptr()), "seq_routed_experts")
+    sm100._count(2)
+    return out
+
+
+def softcap(z, cap):
+    assert z.stride(1) == 1
+    check(_L().gllm_seq_softcap(_p(z), z.stride(0), z.shape[0], z.shape[1], float(cap), _f32(z), stream_ptr()),
+          "seq_softcap")
+    sm100._count()
+    return z
