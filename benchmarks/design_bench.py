@@ -1,9 +1,12 @@
-"""Prefill / decode throughput of the Saritar design beside the closest existing decoder (Qwen3: GQA attention with
-q/k norm + gated MLP) at matched width, depth and parameter count, through the public `LLM.generate` API with
-random weights, plus the device time of each new kernel against its roofline and against the like kernel of the
-existing path. Invoked as `python bench.py --design saritar` (the default benchmark is untouched).
+"""Prefill / decode throughput of a layer-list design beside the closest existing decoder at matched width, depth and
+(roughly) parameter count, through the public `LLM.generate` API with random weights, plus the device time of each
+new kernel against its roofline and against the like kernel of the existing path. Invoked as
+`python bench.py --design saritar|femolix` (the default benchmark is untouched).
 
-Prints ONE JSON line: {"design": ..., "sizes": [{"width", ..., "saritar": {...}, "qwen3": {...}}], "kernels": [...]}
+  saritar  beside Qwen3 (GQA attention with q/k norm + gated MLP)
+  femolix  beside Qwen3-MoE (rotary GQA attention with q/k norm + routed gated experts)
+
+Prints ONE JSON line: {"design": ..., "sizes": [{"width", ..., "<design>": {...}, "<closest>": {...}}], "kernels": [...]}
 """
 from __future__ import annotations
 
@@ -27,6 +30,35 @@ def _saritar_cfg(width, n_pairs, heads, kv, dim, window, ff, vocab):
 def _qwen3_cfg(width, layers, heads, kv, dim, inter, vocab):
     return {"architectures": ["Qwen3ForCausalLM"], "hidden_size": width, "num_hidden_layers": layers,
             "num_attention_heads": heads, "num_key_value_heads": kv, "head_dim": dim, "intermediate_size": inter,
+            "vocab_size": vocab, "rms_norm_eps": 1e-6, "rope_theta": 1e6, "max_position_embeddings": 8192,
+            "tie_word_embeddings": False, "torch_dtype": "bfloat16"}
+
+
+def _femolix_cfg(width, n_quads, vocab, experts=16, top=2):
+    heads = width // 128
+    kv = max(heads // 4, 1)
+    ff_moe = {"kind": "moe", "expert": {"ff": width}, "router": {"experts": experts, "top": top}}
+    delta = {"type": "delta", "mixer": {"conv": 4, "dim": 128, "heads": heads, "kv_heads": max(heads // 2, 1),
+                                        "vdim": 128}, "mlp": ff_moe}
+    rh = max(heads // 2, 1)
+    par = {"type": "parallel",
+           "mixer": {"left": {"dim": 128, "heads": heads, "kv_heads": kv, "vdim": 128, "mask": {"size": 1024},
+                              "rot": {"base": 1e6, "dims": 128}, "scale": 128 ** -0.5},
+                     "right": {"decay": [1.0 - 2.0 ** (-3 - i % 6) for i in range(rh)], "dim": 128, "heads": rh,
+                               "vdim": 128},
+                     "left_scale": 1.0, "right_scale": 1.0}, "mlp": ff_moe}
+    first = {**delta, "mlp": {"kind": "dense", "ff": 3 * width}}
+    layers = ([first, par, par, delta] + [delta, par, par, delta] * (n_quads - 1))
+    return {"architecture": "Femolix", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "postln_alpha": 1.0,
+            "logit_softcap": 30.0, "layers": layers}
+
+
+def _qwen3_moe_cfg(width, layers, vocab, experts=16, top=2):
+    heads = width // 128
+    return {"architectures": ["Qwen3MoeForCausalLM"], "hidden_size": width, "num_hidden_layers": layers,
+            "num_attention_heads": heads, "num_key_value_heads": max(heads // 4, 1), "head_dim": 128,
+            "intermediate_size": 3 * width, "moe_intermediate_size": width, "num_experts": experts,
+            "num_experts_per_tok": top, "norm_topk_prob": True, "decoder_sparse_step": 1, "mlp_only_layers": [0],
             "vocab_size": vocab, "rms_norm_eps": 1e-6, "rope_theta": 1e6, "max_position_embeddings": 8192,
             "tie_word_embeddings": False, "torch_dtype": "bfloat16"}
 
@@ -149,12 +181,146 @@ def _kernels(peaks):
     return out
 
 
+def _kernels_femolix(peaks):
+    """Device time of the kernels this design added, at layer-like sizes, with the like kernel of the existing path."""
+    from gllm_b200.ops import ref, sm100, sm100_seq as S
+    dev, bf = "cuda", torch.bfloat16
+    hbm = float(peaks.get("hbm_gbs", 6650.0))
+    out = []
+
+    def row(name, ms, nbytes, like=None, flops=None):
+        r = {"kernel": name, "ms": round(ms, 4), "gbs": round(nbytes / ms / 1e6, 1),
+             "frac_hbm": round(nbytes / ms / 1e6 / hbm, 3)}
+        if flops:
+            r["tflops"] = round(flops / ms / 1e9, 2)
+        if like:
+            r["like"] = like
+        out.append(r)
+
+    T, W = 8192, 4096
+    x = torch.randn(T, W, device=dev)
+    y, w1 = torch.randn(T, W, device=dev).to(bf), torch.ones(W, device=dev).to(bf)
+    row("postnorm (scale + add + norm, fp32 stream in/out, bf16 in/out)",
+        _time(lambda: S.postnorm(x, y, 1.0, w1, 1e-5, bf)), T * W * (4 + 4 + 2 + 2))
+    res = torch.randn(T, W, device=dev).to(bf)
+    row("rmsnorm + residual (existing bf16 path)", _time(lambda: sm100.rmsnorm(y, w1, 1e-5, res)),
+        T * W * (2 + 2 + 2 + 2), like="postnorm")
+    H, G, D, ps = 32, 8, 128, 16
+    for label, qlens, ctx, ch in (("prefill 4 x 2048, chunk 1024", [2048] * 4, 0, 1024),
+                                  ("decode 256 x 1 at 2048, chunk 1024", [1] * 256, 2047, 1024)):
+        Tt, B = sum(qlens), len(qlens)
+        qsl = torch.tensor([0] + torch.tensor(qlens).cumsum(0).tolist(), dtype=torch.int32, device=dev)
+        sl = torch.tensor([q + ctx for q in qlens], dtype=torch.int32, device=dev)
+        npp = (max(qlens) + ctx + ps - 1) // ps
+        bt = torch.arange(B * npp, dtype=torch.int32, device=dev).reshape(B, npp)
+        kshape = ref.kv_cache_shape(B * npp + 1, G, D, ps)
+        kc, vc = torch.randn(kshape, device=dev).to(bf), torch.randn(kshape, device=dev).to(bf)
+        pos = torch.cat([torch.arange(ctx, ctx + q) for q in qlens]).to(torch.int32).to(dev)
+        seqi = torch.cat([torch.full((q,), i) for i, q in enumerate(qlens)]).to(dev)
+        slots = (bt[seqi, (pos // ps).long()] * ps + pos % ps).to(torch.int32)
+        qkv = torch.randn(Tt, (H + 2 * G) * D, device=dev).to(bf)
+        qn = torch.ones(D, device=dev).to(bf)
+        ms = _time(lambda: S.qk_norm_rope_kv_write(qkv, H, G, D, D, qn, qn, 1e-5, pos, D, 1e6, kc, vc, slots))
+        row("qk_norm_rope_kv_write " + label, ms, Tt * (H + 2 * G) * D * 2 * 2)
+        cs = torch.randn(8192, D, device=dev)
+        qq = qkv[:, :H * D].unflatten(1, (H, D))
+        kk = qkv[:, H * D:(H + G) * D].unflatten(1, (G, D))
+        vv = qkv[:, (H + G) * D:].unflatten(1, (G, D))
+        ms2 = _time(lambda: sm100.rope_kv_write(qq, kk, vv, pos, cs, D, True, qn, qn, 1e-5, kc, vc, slots))
+        row("rope_kv_write (existing: table rotary + q/k norm + cache write) " + label, ms2,
+            Tt * (H + 2 * G) * D * 2 * 2, like="qk_norm_rope_kv_write")
+        q = torch.randn(Tt, H * D, device=dev).to(bf)
+        keys = sum(p % ch + 1 for ql in qlens for p in range(ctx, ctx + ql))
+        nd = B if qlens[0] == 1 else 0
+        ms = _time(lambda: S.window_attention(q, kc, vc, bt, sl, qsl, pos, D ** -0.5, H, D, None, None,
+                                              num_decode_seqs=nd, max_q_len=max(qlens), chunk=ch, v_dim=D), iters=5)
+        r = {"kernel": "chunk attention " + label, "ms": round(ms, 4),
+             "tflops": round(4.0 * keys * H * D / ms / 1e9, 2)}
+        ms2 = _time(lambda: sm100.paged_attention(q, kc, vc, bt, sl, qsl, D ** -0.5, H, D,
+                                                  B if qlens[0] == 1 else 0, B, max(qlens), max(qlens) + ctx), iters=3)
+        full = sum(p + 1 for ql in qlens for p in range(ctx, ctx + ql))
+        r["like"] = {"kernel": "paged_attention (existing, full causal)", "ms": round(ms2, 4),
+                     "tflops": round(4.0 * full * H * D / ms2 / 1e9, 2)}
+        out.append(r)
+    Hh, Gq, Dd, V = 32, 16, 128, 128
+    for label, qlens in (("prefill 4 x 2048", [2048] * 4), ("decode 256 x 1", [1] * 256)):
+        Tt, B = sum(qlens), len(qlens)
+        qsl = torch.tensor([0] + torch.tensor(qlens).cumsum(0).tolist(), dtype=torch.int32, device=dev)
+        sl = torch.tensor([q + 100 for q in qlens], dtype=torch.int32, device=dev)
+        rs = torch.arange(B, dtype=torch.int32, device=dev)
+        qk = torch.randn(Tt, 2 * Gq * Dd, device=dev).to(bf)
+        v = torch.randn(Tt, Hh * V, device=dev).to(bf)
+        ba = torch.randn(Tt, 2 * Hh, device=dev).to(bf)
+        na, db = -torch.rand(Hh, device=dev), torch.randn(Hh, device=dev)
+        st = torch.zeros(B, Hh, Dd, V, device=dev)
+        nbytes = Tt * (2 * Gq * Dd + Hh * V) * 2 + Tt * Hh * V * 4 + B * Hh * Dd * V * 8
+        flops = 6.0 * Tt * Hh * Dd * V
+        row("linear_state_scan (gated delta rule) " + label,
+            _time(lambda: S.linear_state_scan(qk[:, :Gq * Dd], qk[:, Gq * Dd:], v, ba[:, :Hh], ba[:, Hh:], na, db, None,
+                                              st, rs, sl, qsl, Hh, Gq, Dd, V, False, True, Dd ** -0.5, True), iters=5),
+            nbytes, flops=flops)
+        dec = torch.full((Hh,), 0.99, device=dev)
+        qk2 = torch.randn(Tt, 2 * Hh * Dd, device=dev).to(bf)
+        row("linear_state_scan (constant decay) " + label,
+            _time(lambda: S.linear_state_scan(qk2[:, :Hh * Dd], qk2[:, Hh * Dd:], v, None, None, None, None, dec, st, rs,
+                                              sl, qsl, Hh, Hh, Dd, V, True, False, 1.0, False), iters=5),
+            Tt * (2 * Hh * Dd + Hh * V) * 2 + Tt * Hh * V * 4 + B * Hh * Dd * V * 8, flops=4.0 * Tt * Hh * Dd * V)
+        o = torch.randn(Tt, Hh * V, device=dev)
+        gate, nw = torch.randn(Tt, Hh * V, device=dev).to(bf), torch.ones(V, device=dev).to(bf)
+        row("gated_group_norm (per head) " + label,
+            _time(lambda: S.gated_group_norm(o, gate, nw, V, 1e-5, "silu")), Tt * Hh * V * (4 + 2 + 2))
+    C, N, R = 8192, 16, 256
+    qlens = [2048] * 4
+    Tt, B = sum(qlens), len(qlens)
+    qsl = torch.tensor([0] + torch.tensor(qlens).cumsum(0).tolist(), dtype=torch.int32, device=dev)
+    sl = torch.tensor([q + 100 for q in qlens], dtype=torch.int32, device=dev)
+    rs = torch.arange(B, dtype=torch.int32, device=dev)
+    xz = torch.randn(Tt, 2 * C, device=dev).to(bf)
+    xc = torch.randn(Tt, C, device=dev).to(bf)
+    proj, dtr = torch.randn(Tt, R + 2 * N, device=dev).to(bf), torch.randn(Tt, C, device=dev).to(bf)
+    A, Dk, db2 = -torch.rand(C, N, device=dev), torch.randn(C, device=dev), torch.randn(C, device=dev)
+    ss = torch.zeros(B, N, C, device=dev)
+    row("selective_scan (existing recurrent kernel) prefill 4 x 2048, 8192 ch x 16",
+        _time(lambda: S.selective_scan(xc, dtr, proj, xz, A, Dk, db2, ss, rs, sl, qsl, C, N, R), iters=5),
+        Tt * C * 2 * 4 + B * N * C * 8, like="linear_state_scan", flops=4.0 * Tt * C * N)
+    T2, E = 8192, 64
+    hh, wr = torch.randn(T2, W, device=dev).to(bf), torch.randn(E, W, device=dev).to(bf)
+    row("router_topk (fp32 logits + top-2 + softmax) 8192 x 4096 x 64", _time(lambda: S.router_topk(hh, wr, 2)),
+        T2 * W * 2 + E * W * 2)
+    from gllm_b200.ops import sm100_moe
+    row("router GEMM + topk_softmax (existing)",
+        _time(lambda: sm100_moe.topk_softmax(sm100.linear(hh, wr), 2, True)), T2 * W * 2 + E * W * 2, like="router_topk")
+    gu = torch.randn(T2, 2 * 12288, device=dev).to(bf)
+    row("silu_mul 8192 x 12288", _time(lambda: S.silu_mul(gu)), T2 * 12288 * 6)
+    row("silu_and_mul (existing)", _time(lambda: sm100.silu_and_mul(gu)), T2 * 12288 * 6, like="silu_mul")
+    return out
+
+
+def run_femolix(args, peaks):
+    vocab = 32000
+    kernels = _kernels_femolix(peaks)
+    sizes = []
+    for width, quads in ((1024, 2), (2048, 2), (4096, 1)):
+        f_cfg = _femolix_cfg(width, quads, vocab)
+        q_cfg = _qwen3_moe_cfg(width, 4 * quads, vocab)
+        sizes.append({"width": width, "layers": 4 * quads,
+                      "femolix": _throughput(f_cfg, vocab, args.warmup, args.steps),
+                      "qwen3_moe": _throughput(q_cfg, vocab, args.warmup, args.steps)})
+    line = {"design": "femolix", "dtype": "bf16", "data": "synthetic", "warmup": args.warmup, "steps": args.steps,
+            "timing": "wall clock around LLM.generate with synchronize (sizes); CUDA events, L2 flushed (kernels)",
+            "peaks": peaks, "sizes": sizes, "kernels": kernels}
+    print(json.dumps(line))
+    return line
+
+
 def run(args):
     peaks = {}
     p = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
     if os.path.exists(p):
         with open(p) as f:
             peaks = json.load(f)
+    if getattr(args, "design", "saritar") == "femolix":
+        return run_femolix(args, peaks)
     vocab = 32000
     kernels = _kernels(peaks)
     sizes = []

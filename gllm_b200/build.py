@@ -4,7 +4,11 @@ Plain `nvcc` -> one shared object with a C ABI (loaded through ctypes in
 `gllm_b200.ops.lib`). No torch headers are needed, so a full rebuild takes
 seconds and cross-compiles on a GPU-less box.
 
-    python -m gllm_b200.build [--force] [--verbose]
+    python -m gllm_b200.build [--force] [--verbose] [--groups seq,gemm,...]
+
+`groups` (sub-directories of csrc/) builds a library that holds only those kernel families: a first call in a
+fresh checkout then compiles what its model needs and nothing else. `build.stamp` records which groups the library
+holds; `ops.lib.load` completes it when a later caller needs more.
 """
 from __future__ import annotations
 
@@ -29,13 +33,30 @@ NVCC_FLAGS = [
 ]
 
 
-def _sources() -> list[str]:
+def _sources(groups=None) -> list[str]:
     out = []
     for d, _, files in os.walk(CSRC):
+        if groups is not None and os.path.relpath(d, CSRC).split(os.sep)[0] not in groups:
+            continue
         for f in sorted(files):
             if f.endswith(".cu") or f.endswith(".cpp"):
                 out.append(os.path.join(d, f))
     return sorted(out)
+
+
+def all_groups() -> set:
+    return {os.path.relpath(os.path.dirname(s), CSRC).split(os.sep)[0] for s in _sources()}
+
+
+def built_groups():
+    """Groups the library on disk holds (None: no library, or one from before groups were recorded = everything)."""
+    stamp = os.path.join(OUT_DIR, "build.stamp")
+    if not os.path.exists(LIB_PATH) or not os.path.exists(stamp):
+        return None
+    lines = open(stamp).read().split("\n")
+    if len(lines) < 2 or not lines[1].startswith("groups="):
+        return all_groups()
+    return set(g for g in lines[1][len("groups="):].split(",") if g)
 
 
 def _headers() -> list[str]:
@@ -67,9 +88,15 @@ def nvcc_path() -> str:
     return "nvcc"
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
+def build(force: bool = False, verbose: bool = False, groups=None) -> str:
     os.makedirs(OUT_DIR, exist_ok=True)
-    srcs = _sources()
+    if groups is not None:
+        groups = set(groups) & all_groups()
+        if groups == all_groups():
+            groups = None
+    srcs = _sources(groups)
+    held = built_groups()
+    want = all_groups() if groups is None else groups
     hdr_digest = _digest(_headers())
     stamp_path = os.path.join(OUT_DIR, "build.stamp")
     objs = []
@@ -107,19 +134,22 @@ def build(force: bool = False, verbose: bool = False) -> str:
         with ThreadPoolExecutor(max_workers=min(8, len(todo))) as ex:
             for s in ex.map(compile_one, todo):
                 print(f"[gllm_b200.build] compiled {os.path.relpath(s, ROOT)}")
-    if todo or not os.path.exists(LIB_PATH):
+    if todo or not os.path.exists(LIB_PATH) or held != want:
         cmd = [nvcc_path(), "-shared", "-o", LIB_PATH, *objs, "-lpthread"]  # static cudart (nvcc default)
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
         print(f"[gllm_b200.build] linked {LIB_PATH}")
         with open(stamp_path, "w") as f:
-            f.write(hdr_digest)
+            f.write(hdr_digest + "\ngroups=" + ",".join(sorted(want)))
     return LIB_PATH
 
 
 def main():
-    build(force="--force" in sys.argv, verbose="--verbose" in sys.argv)
+    groups = None
+    if "--groups" in sys.argv:
+        groups = sys.argv[sys.argv.index("--groups") + 1].split(",")
+    build(force="--force" in sys.argv, verbose="--verbose" in sys.argv, groups=groups)
 
 
 if __name__ == "__main__":

@@ -39,6 +39,11 @@ struct AttnParams {
   // logit per query head in the softmax denominator that carries no value (null = none; decode: num_splits == 1)
   int window;
   const float* sink;
+  // chunk mask: a query at position i sees only keys j with floor(j / chunk) == floor(i / chunk) (0 = none);
+  // the result is multiplied by out_scale and written with a token stride of out_ts elements (num_splits == 1)
+  int chunk;
+  int64_t out_ts;
+  float out_scale;
 };
 
 template <int D>
@@ -102,7 +107,8 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_cons
   const int split = blockIdx.z;
   const int seq_len = p.seq_lens[seq];
   const int n_tiles = (seq_len + kTileN - 1) / kTileN;
-  const int win_lo = p.window > 0 ? max(0, seq_len - p.window) : 0;   // first visible key
+  int win_lo = p.window > 0 ? max(0, seq_len - p.window) : 0;   // first visible key
+  if (p.chunk > 0) win_lo = max(win_lo, ((seq_len - 1) / p.chunk) * p.chunk);
   const int tile_lo = win_lo / kTileN;
   const int tps = (n_tiles - tile_lo + p.num_splits - 1) / p.num_splits;
   const int tile_begin = min(tile_lo + split * tps, n_tiles);
@@ -271,7 +277,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_cons
     const int head = hbase + row;
     if (p.sink != nullptr && p.num_splits == 1 && m_all > -INFINITY)
       l_all += exp2f(p.sink[head] * 1.4426950408889634f - m_all);
-    const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
+    const float inv = (l_all > 0.f ? 1.f / l_all : 0.f) * p.out_scale;
     for (int c = (tid & 7) * 4; c < D; c += 32) {
       float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
@@ -282,7 +288,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_cons
       acc.x *= inv; acc.y *= inv; acc.z *= inv; acc.w *= inv;
       if (p.num_splits == 1) {
         uint2 ov = make_uint2(pack_bf16(acc.x, acc.y), pack_bf16(acc.z, acc.w));
-        *reinterpret_cast<uint2*>(p.out + ((size_t)seq * p.Hq + head) * D + c) = ov;
+        *reinterpret_cast<uint2*>(p.out + (size_t)seq * p.out_ts + (size_t)head * D + c) = ov;
       } else {
         *reinterpret_cast<float4*>(p.part_o + (((size_t)seq * p.Hq + head) * p.num_splits + split) * D + c) = acc;
       }
@@ -386,7 +392,8 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
   const int last_tok = min(tok_base + toks_per_tile, q_len) - 1;
   const int kv_end = ctx_len + last_tok + 1;  // causal horizon of this tile
   const int n_tiles = (kv_end + kTileN - 1) / kTileN;
-  const int tile_lo = p.window > 0 ? max(0, ctx_len + tok_base - p.window + 1) / kTileN : 0;   // first query's window
+  int tile_lo = p.window > 0 ? max(0, ctx_len + tok_base - p.window + 1) / kTileN : 0;   // first query's window
+  if (p.chunk > 0) tile_lo = max(tile_lo, (((ctx_len + tok_base) / p.chunk) * p.chunk) / kTileN);
   const int page_bytes = p.page_size * D * 2;
 
   if (threadIdx.x == 0) {
@@ -434,6 +441,8 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
   float m_run[2] = {-INFINITY, -INFINITY};
   float l_run[2] = {0.f, 0.f};
   const int lim[2] = {ctx_len + r_tok[0], ctx_len + r_tok[1]};  // last visible key per row
+  const int clo[2] = {p.chunk > 0 ? (max(lim[0], 0) / p.chunk) * p.chunk : 0,
+                      p.chunk > 0 ? (max(lim[1], 0) / p.chunk) * p.chunk : 0};   // first key of the row's chunk
 
   uint32_t it = 0;
   for (int tile = tile_lo; tile < n_tiles; ++tile, ++it) {
@@ -466,7 +475,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
       for (int e = 0; e < 4; ++e) {
         const int col = abs0 + nt * 8 + (e & 1);
         float v = sc[nt][e] * p.scale_log2;
-        if (col > lim[e >> 1] || (p.window > 0 && col <= lim[e >> 1] - p.window)) v = -INFINITY;
+        if (col > lim[e >> 1] || col < clo[e >> 1] || (p.window > 0 && col <= lim[e >> 1] - p.window)) v = -INFINITY;
         sc[nt][e] = v;
         mx[e >> 1] = fmaxf(mx[e >> 1], v);
       }
@@ -528,8 +537,8 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
     if (!r_ok[r]) continue;
     float den = l_run[r];
     if (p.sink != nullptr && m_run[r] > -INFINITY) den += exp2f(p.sink[r_head[r]] * 1.4426950408889634f - m_run[r]);
-    const float inv = den > 0.f ? 1.f / den : 0.f;
-    __nv_bfloat16* op = p.out + ((size_t)(q_begin + r_tok[r]) * p.Hq + r_head[r]) * D + 2 * t;
+    const float inv = (den > 0.f ? 1.f / den : 0.f) * p.out_scale;
+    __nv_bfloat16* op = p.out + (size_t)(q_begin + r_tok[r]) * p.out_ts + (size_t)r_head[r] * D + 2 * t;
 #pragma unroll
     for (int nd = 0; nd < D / 8; ++nd) {
       *reinterpret_cast<uint32_t*>(op + nd * 8) = pack_bf16(o[nd][2 * r] * inv, o[nd][2 * r + 1] * inv);
@@ -595,7 +604,7 @@ static int attn_decode_impl(const void* q, int64_t q_ts, void* out, const void* 
                             int64_t num_pages, const void* block_table, const void* seq_lens, void* part_o,
                             void* part_lse, int num_seqs, int seq_offset, int max_blocks, int Hq, int Hkv,
                             int D, int page_size, int num_splits, float scale, void* split_cnt, void* stream,
-                            int window, const void* sink) {
+                            int window, const void* sink, int chunk = 0, int64_t out_ts = 0, float out_scale = 1.0f) {
   if (sink != nullptr && num_splits > 1) {
     fprintf(stderr, "[gllm_b200] attn_decode: a softmax sink needs num_splits == 1\n");
     return 1;
@@ -623,6 +632,11 @@ static int attn_decode_impl(const void* q, int64_t q_ts, void* out, const void* 
   p.scale_log2 = scale * 1.4426950408889634f;
   p.split_cnt = reinterpret_cast<uint32_t*>(split_cnt);
   p.window = window; p.sink = reinterpret_cast<const float*>(sink);
+  p.chunk = chunk; p.out_ts = out_ts > 0 ? out_ts : (int64_t)Hq * D; p.out_scale = out_scale;
+  if ((chunk > 0 || out_scale != 1.0f || p.out_ts != (int64_t)Hq * D) && p.num_splits > 1) {
+    fprintf(stderr, "[gllm_b200] attn_decode: chunk mask / scaled or strided output need num_splits == 1\n");
+    return 1;
+  }
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   int rc;
   switch (D) {
@@ -669,7 +683,7 @@ static int attn_prefill_impl(const void* q, int64_t q_ts, void* out, const void*
                              int64_t num_pages, const void* block_table, const void* seq_lens,
                              const void* q_start, int num_seqs, int seq_offset, int max_q_len, int max_blocks,
                              int Hq, int Hkv, int D, int page_size, float scale, void* stream, int window,
-                             const void* sink) {
+                             const void* sink, int chunk = 0, int64_t out_ts = 0, float out_scale = 1.0f) {
   if (num_seqs <= 0 || max_q_len <= 0) return 0;
   if (page_size < 8 || kTileN % page_size != 0 || Hq % Hkv != 0) {
     fprintf(stderr, "[gllm_b200] attn_prefill: unsupported page_size=%d / heads\n", page_size);
@@ -690,6 +704,7 @@ static int attn_prefill_impl(const void* q, int64_t q_ts, void* out, const void*
   p.page_size = page_size; p.num_splits = 1; p.seq_offset = seq_offset;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.split_cnt = nullptr; p.window = window; p.sink = reinterpret_cast<const float*>(sink);
+  p.chunk = chunk; p.out_ts = out_ts > 0 ? out_ts : (int64_t)Hq * D; p.out_scale = out_scale;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   switch (D) {
     case 64: return launch_prefill<64>(tk, tv, p, num_seqs, max_q_len, st);
@@ -716,4 +731,26 @@ GLLM_EXPORT int gllm_attn_prefill_win(const void* q, int64_t q_ts, void* out, co
                                       float scale, int window, const void* sink, void* stream) {
   return attn_prefill_impl(q, q_ts, out, k_cache, v_cache, num_pages, block_table, seq_lens, q_start, num_seqs,
                            seq_offset, max_q_len, max_blocks, Hq, Hkv, D, page_size, scale, stream, window, sink);
+}
+
+// window + chunk mask + sink, result times out_scale, output rows out_ts elements apart (2-byte aligned to 8 bytes)
+GLLM_EXPORT int gllm_attn_decode_mask(const void* q, int64_t q_ts, void* out, int64_t out_ts, const void* k_cache,
+                                      const void* v_cache, int64_t num_pages, const void* block_table,
+                                      const void* seq_lens, int num_seqs, int seq_offset, int max_blocks, int Hq,
+                                      int Hkv, int D, int page_size, float scale, int window, int chunk,
+                                      const void* sink, float out_scale, void* stream) {
+  return attn_decode_impl(q, q_ts, out, k_cache, v_cache, num_pages, block_table, seq_lens, nullptr, nullptr,
+                          num_seqs, seq_offset, max_blocks, Hq, Hkv, D, page_size, 1, scale, nullptr, stream, window,
+                          sink, chunk, out_ts, out_scale);
+}
+
+GLLM_EXPORT int gllm_attn_prefill_mask(const void* q, int64_t q_ts, void* out, int64_t out_ts, const void* k_cache,
+                                       const void* v_cache, int64_t num_pages, const void* block_table,
+                                       const void* seq_lens, const void* q_start, int num_seqs, int seq_offset,
+                                       int max_q_len, int max_blocks, int Hq, int Hkv, int D, int page_size,
+                                       float scale, int window, int chunk, const void* sink, float out_scale,
+                                       void* stream) {
+  return attn_prefill_impl(q, q_ts, out, k_cache, v_cache, num_pages, block_table, seq_lens, q_start, num_seqs,
+                           seq_offset, max_q_len, max_blocks, Hq, Hkv, D, page_size, scale, stream, window, sink,
+                           chunk, out_ts, out_scale);
 }

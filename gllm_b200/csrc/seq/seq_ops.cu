@@ -303,9 +303,9 @@ __global__ void relu2_kernel(const T* __restrict__ x, T* __restrict__ out, size_
 }
 
 // C[M, N] = A[M, K] . W[N, K]^T, fp32 accumulation in ascending k for every element
-template <typename T>
+template <typename T, typename TO = T>
 __global__ void __launch_bounds__(256) gemm_simt_kernel(const T* __restrict__ A, long lda, const T* __restrict__ W,
-                                                        long ldw, T* __restrict__ Cm, long ldc, int M, int N, int K) {
+                                                        long ldw, TO* __restrict__ Cm, long ldc, int M, int N, int K) {
   __shared__ float As[16][64 + 1], Ws[16][64 + 1];
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
   const int m0 = blockIdx.y * 64, n0 = blockIdx.x * 64;
@@ -334,7 +334,7 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const T* __restrict__ A,
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int m = m0 + ty * 4 + i, n = n0 + tx * 4 + j;
-      if (m < M && n < N) Cm[(size_t)m * ldc + n] = from_f<T>(acc[i][j]);
+      if (m < M && n < N) Cm[(size_t)m * ldc + n] = from_f<TO>(acc[i][j]);
     }
 }
 
@@ -534,6 +534,22 @@ GLLM_EXPORT int gllm_seq_gemm_simt(const void* a, long lda, const void* w, long 
                                                                       (__nv_bfloat16*)c, ldc, M, N, K)),
                 (gemm_simt_kernel<float><<<grid, 256, 0, st>>>((const float*)a, lda, (const float*)w, ldw, (float*)c,
                                                                ldc, M, N, K)));
+  CUDA_CHECK_RET(cudaGetLastError());
+  return 0;
+}
+
+// the same product with the result kept in fp32 whatever the operand dtype (router logits)
+GLLM_EXPORT int gllm_seq_gemm_simt_f32out(const void* a, long lda, const void* w, long ldw, void* c, long ldc, int M,
+                                          int N, int K, int is_f32, void* stream) {
+  if (M <= 0 || N <= 0) return 0;
+  cudaStream_t st = (cudaStream_t)stream;
+  dim3 grid((N + 63) / 64, (M + 63) / 64);
+  GLLM_BY_DTYPE(is_f32,
+                (gemm_simt_kernel<__nv_bfloat16, float><<<grid, 256, 0, st>>>((const __nv_bfloat16*)a, lda,
+                                                                             (const __nv_bfloat16*)w, ldw, (float*)c,
+                                                                             ldc, M, N, K)),
+                (gemm_simt_kernel<float, float><<<grid, 256, 0, st>>>((const float*)a, lda, (const float*)w, ldw,
+                                                                      (float*)c, ldc, M, N, K)));
   CUDA_CHECK_RET(cudaGetLastError());
   return 0;
 }

@@ -41,47 +41,55 @@ __global__ void __launch_bounds__(256) postnorm_kernel(float* __restrict__ x, co
   }
 }
 
-// One warp per (token, head): heads [0, H) queries, [H, H + G) keys, [H + G, H + 2G) values (copied to the V cache).
-// q / k: RMS norm over D with a shared weight, then entries i and i + rot/2 (i < rot/2) turn by pos * base^(-2i/rot).
-// The angle is formed in fp64 (no table, no maximum position), the rotation itself in fp32.
+// One block per token; its warps walk the heads: [0, H) queries, [H, H + G) keys, [H + G, H + 2G) values (copied to
+// the V cache). q / k: RMS norm over D with a shared weight, then entries i and i + rot/2 (i < rot/2) turn by
+// pos * base^(-2i/rot). The token's cos / sin row is formed once per block, the angle in fp64 (no table, no maximum
+// position), the rotation itself in fp32.
 template <typename T>
-__global__ void qk_norm_rope_kv_write_kernel(const T* __restrict__ qkv, long ld, int H, int G, int D, int Dv,
-                                             const T* __restrict__ qn, const T* __restrict__ kn, float eps,
-                                             const int* __restrict__ positions, int rot, double log2_base,
-                                             T* __restrict__ q_out, T* __restrict__ kc, T* __restrict__ vc,
-                                             const int* __restrict__ slots, int ps, int slab, int slab_v) {
+__global__ void __launch_bounds__(128) qk_norm_rope_kv_write_kernel(
+    const T* __restrict__ qkv, long ld, int H, int G, int D, int Dv, const T* __restrict__ qn,
+    const T* __restrict__ kn, float eps, const int* __restrict__ positions, int rot, double log2_base,
+    T* __restrict__ q_out, T* __restrict__ kc, T* __restrict__ vc, const int* __restrict__ slots, int ps, int slab,
+    int slab_v) {
+  extern __shared__ float cs_tab[];      // [rot / 2] cos, then [rot / 2] sin
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int head = blockIdx.y * 4 + warp, t = blockIdx.x;
-  if (head >= H + 2 * G) return;
-  const int slot = slots[t];
-  if (head >= H + G) {
-    if (slot < 0) return;
-    const int g = head - H - G;
-    const T* src = qkv + (size_t)t * ld + (size_t)(H + G) * D + (size_t)g * Dv;
-    for (int d = lane; d < Dv; d += 32) vc[cache_index(slot, g, d, G, Dv, ps, slab_v)] = src[d];
-    return;
-  }
-  const T* src = qkv + (size_t)t * ld + (size_t)head * D;
-  float ss = 0.f;
-  for (int d = lane; d < D; d += 32) { const float v = to_f(src[d]); ss += v * v; }
-  ss = warp_sum(ss);
-  const T* w = head < H ? qn : kn;
-  const float r = w != nullptr ? 1.0f / sqrtf(ss / (float)D + eps) : 1.0f;
+  const int t = blockIdx.x;
   const int half = rot / 2;
   const double pos = (double)positions[t];
-  if (head >= H && slot < 0) return;
-  for (int d = lane; d < D; d += 32) {
-    float v = to_f(src[d]) * r * (w != nullptr ? to_f(w[d]) : 1.0f);
-    if (d < rot) {
-      const int i = d < half ? d : d - half, pd = d < half ? d + half : d - half;
-      const float other = to_f(src[pd]) * r * (w != nullptr ? to_f(w[pd]) : 1.0f);
-      double sn, cs;
-      sincos(pos * exp2(-(2.0 * (double)i / (double)rot) * log2_base), &sn, &cs);
-      const float c = (float)cs, s = (float)sn;
-      v = d < half ? v * c - other * s : v * c + other * s;
+  for (int i = threadIdx.x; i < half; i += 128) {
+    double sn, cs;
+    sincos(pos * exp2(-(2.0 * (double)i / (double)rot) * log2_base), &sn, &cs);
+    cs_tab[i] = (float)cs;
+    cs_tab[half + i] = (float)sn;
+  }
+  __syncthreads();
+  const int slot = slots[t];
+  for (int head = warp; head < H + 2 * G; head += 4) {
+    if (head >= H + G) {
+      if (slot < 0) continue;
+      const int g = head - H - G;
+      const T* src = qkv + (size_t)t * ld + (size_t)(H + G) * D + (size_t)g * Dv;
+      for (int d = lane; d < Dv; d += 32) vc[cache_index(slot, g, d, G, Dv, ps, slab_v)] = src[d];
+      continue;
     }
-    if (head < H) q_out[(size_t)t * H * D + (size_t)head * D + d] = from_f<T>(v);
-    else kc[cache_index(slot, head - H, d, G, D, ps, slab)] = from_f<T>(v);
+    if (head >= H && slot < 0) continue;
+    const T* src = qkv + (size_t)t * ld + (size_t)head * D;
+    float ss = 0.f;
+    for (int d = lane; d < D; d += 32) { const float v = to_f(src[d]); ss += v * v; }
+    ss = warp_sum(ss);
+    const T* w = head < H ? qn : kn;
+    const float r = w != nullptr ? 1.0f / sqrtf(ss / (float)D + eps) : 1.0f;
+    for (int d = lane; d < D; d += 32) {
+      float v = to_f(src[d]) * r * (w != nullptr ? to_f(w[d]) : 1.0f);
+      if (d < rot) {
+        const int i = d < half ? d : d - half, pd = d < half ? d + half : d - half;
+        const float other = to_f(src[pd]) * r * (w != nullptr ? to_f(w[pd]) : 1.0f);
+        const float c = cs_tab[i], sn = cs_tab[half + i];
+        v = d < half ? v * c - other * sn : v * c + other * sn;
+      }
+      if (head < H) q_out[(size_t)t * H * D + (size_t)head * D + d] = from_f<T>(v);
+      else kc[cache_index(slot, head - H, d, G, D, ps, slab)] = from_f<T>(v);
+    }
   }
 }
 
@@ -235,31 +243,24 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, long ld, int F, T* __r
   out[i] = from_f<T>(silu_f(to_f(gu[t * ld + f])) * to_f(gu[t * ld + F + f]));
 }
 
-// One block per token: fp32 logits (one expert per warp at a time, lanes over the width, fixed order), then warp 0
-// picks the top_k largest (ties: the lower index) and softmaxes over the chosen logits only.
-template <typename T>
-__global__ void __launch_bounds__(128) router_topk_kernel(const T* __restrict__ h, long ldh, const T* __restrict__ w,
-                                                          int width, int E, int top_k, float* __restrict__ wout,
-                                                          int* __restrict__ ids) {
-  extern __shared__ float logit[];     // [E] then chosen values [top_k]
-  float* chosen = logit + E;
-  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const T* hr = h + (size_t)t * ldh;
-  for (int e = warp; e < E; e += 4) {
-    const T* wr = w + (size_t)e * width;
-    float acc = 0.f;
-    for (int i = lane; i < width; i += 32) acc = fmaf(to_f(hr[i]), to_f(wr[i]), acc);
-    acc = warp_sum(acc);
-    if (lane == 0) logit[e] = acc;
-  }
-  __syncthreads();
-  if (warp != 0) return;
+// Router, second half: one warp per token over its fp32 logits [E] (the first half is the fp32-output GEMM): the
+// top_k largest (ties: the lower index), then softmax over the chosen logits only. A lane owns experts lane,
+// lane + 32, ...; chosen experts are tracked in a per-lane bit mask (E <= 1024).
+__global__ void __launch_bounds__(128) router_select_kernel(const float* __restrict__ logits, int ntok, int E,
+                                                            int top_k, float* __restrict__ wout,
+                                                            int* __restrict__ ids) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * 4 + warp;
+  if (t >= ntok) return;
+  const float* z = logits + (size_t)t * E;
+  unsigned taken = 0u;                   // bit j: expert lane + 32 j is chosen
+  float m = 0.f, den = 0.f;
   for (int kk = 0; kk < top_k; ++kk) {
     float best = -INFINITY;
     int bi = 0x7fffffff;
-    for (int e = lane; e < E; e += 32) {
-      const float v = logit[e];
-      if (v > best) { best = v; bi = e; }
+    for (int e = lane, j = 0; e < E; e += 32, ++j) {
+      const float v = z[e];
+      if (!((taken >> j) & 1u) && v > best) { best = v; bi = e; }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
@@ -267,20 +268,23 @@ __global__ void __launch_bounds__(128) router_topk_kernel(const T* __restrict__ 
       const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
       if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
     }
-    if (bi >= E) bi = kk < E ? kk : 0;           // only when every remaining logit is -inf / NaN
-    if (lane == 0) {
-      chosen[kk] = best;
-      ids[(size_t)t * top_k + kk] = bi;
-      logit[bi] = -INFINITY;
+    if (bi >= E) {                       // only when every remaining logit is -inf / NaN: the first free expert
+      int cand = 0x7fffffff;
+      for (int e = lane, j = 0; e < E; e += 32, ++j)
+        if (!((taken >> j) & 1u)) { cand = e; break; }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) cand = min(cand, __shfl_xor_sync(0xffffffffu, cand, o));
+      bi = cand;
     }
-    __syncwarp();
+    if ((bi & 31) == lane) taken |= 1u << (bi >> 5);
+    if (kk == 0) m = best;               // the first pick is the largest
+    const float p = expf(best - m);
+    den += p;
+    if (lane == 0) { ids[(size_t)t * top_k + kk] = bi; wout[(size_t)t * top_k + kk] = p; }
   }
-  if (lane == 0) {
-    const float m = chosen[0];                   // the first pick is the largest
-    float den = 0.f;
-    for (int kk = 0; kk < top_k; ++kk) { chosen[kk] = expf(chosen[kk] - m); den += chosen[kk]; }
-    for (int kk = 0; kk < top_k; ++kk) wout[(size_t)t * top_k + kk] = chosen[kk] / den;
-  }
+  __syncwarp();
+  if (lane == 0)
+    for (int kk = 0; kk < top_k; ++kk) wout[(size_t)t * top_k + kk] /= den;
 }
 
 // plain experts, first half: act[slot, f] = silu(gate_e[f] . h) * (up_e[f] . h); one warp per (slot, f)
@@ -381,13 +385,14 @@ GLLM_EXPORT int gllm_seq_qk_norm_rope_kv_write(const void* qkv, long ld, int nto
                                                void* stream) {
   if (ntok <= 0) return 0;
   cudaStream_t st = (cudaStream_t)stream;
-  dim3 grid(ntok, (H + 2 * G + 3) / 4);
+  dim3 grid(ntok);
+  const size_t smem = (size_t)(rot > 0 ? rot : 2) * sizeof(float);
   GLLM_BY_DTYPE(is_f32,
-                (qk_norm_rope_kv_write_kernel<bf16_t><<<grid, 128, 0, st>>>(
+                (qk_norm_rope_kv_write_kernel<bf16_t><<<grid, 128, smem, st>>>(
                     (const bf16_t*)qkv, ld, H, G, D, Dv, (const bf16_t*)qn, (const bf16_t*)kn, eps,
                     (const int*)positions, rot, log2_base, (bf16_t*)q_out, (bf16_t*)kc, (bf16_t*)vc,
                     (const int*)slots, ps, slab, slab_v)),
-                (qk_norm_rope_kv_write_kernel<float><<<grid, 128, 0, st>>>(
+                (qk_norm_rope_kv_write_kernel<float><<<grid, 128, smem, st>>>(
                     (const float*)qkv, ld, H, G, D, Dv, (const float*)qn, (const float*)kn, eps,
                     (const int*)positions, rot, log2_base, (float*)q_out, (float*)kc, (float*)vc, (const int*)slots,
                     ps, slab, slab_v)));
@@ -452,17 +457,12 @@ GLLM_EXPORT int gllm_seq_silu_mul(const void* gu, long ld, int ntok, int F, void
   return 0;
 }
 
-GLLM_EXPORT int gllm_seq_router_topk(const void* h, long ldh, const void* w, int ntok, int width, int E, int top_k,
-                                     void* wout, void* ids, int is_f32, void* stream) {
+GLLM_EXPORT int gllm_seq_router_select(const void* logits, int ntok, int E, int top_k, void* wout, void* ids,
+                                       void* stream) {
   if (ntok <= 0) return 0;
-  if (top_k > E || E > 8192) return 2;
+  if (top_k > E || E > 1024) return 2;
   cudaStream_t st = (cudaStream_t)stream;
-  const size_t smem = (size_t)(E + top_k) * sizeof(float);
-  GLLM_BY_DTYPE(is_f32,
-                (router_topk_kernel<bf16_t><<<ntok, 128, smem, st>>>((const bf16_t*)h, ldh, (const bf16_t*)w, width, E,
-                                                                     top_k, (float*)wout, (int*)ids)),
-                (router_topk_kernel<float><<<ntok, 128, smem, st>>>((const float*)h, ldh, (const float*)w, width, E,
-                                                                    top_k, (float*)wout, (int*)ids)));
+  router_select_kernel<<<(ntok + 3) / 4, 128, 0, st>>>((const float*)logits, ntok, E, top_k, (float*)wout, (int*)ids);
   CUDA_CHECK_RET(cudaGetLastError());
   return 0;
 }

@@ -91,6 +91,19 @@ class TraceSession:
         return out
 
 
+def _require_kernels(model_dir: str):
+    """Layer-list decoders use the GEMM, attention, expert and sequence kernels only: in a checkout without a built
+    library the first call then compiles just those families."""
+    try:
+        with open(os.path.join(model_dir, "config.json")) as f:
+            cfg = json.load(f)
+    except OSError:
+        return
+    if cfg.get("architecture") in ("Saritar", "Femolix"):
+        from gllm_b200.ops import lib
+        lib.require({"seq", "gemm", "attn", "moe"})
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="trace_run")
     ap.add_argument("--model", required=True)
@@ -101,6 +114,7 @@ def main(argv=None) -> int:
     ap.add_argument("--page-size", type=int, default=16)
     ap.add_argument("--state-slots", type=int, default=4)
     a = ap.parse_args(argv)
+    _require_kernels(a.model)
     sess = TraceSession(a.model, a.dtype, a.max_tokens, a.device, a.page_size, a.state_slots)
     os.makedirs(a.out, exist_ok=True)
     for line in sys.stdin:

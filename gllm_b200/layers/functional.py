@@ -211,6 +211,8 @@ def gated_group_norm(o, gate, w, group, eps, act, out_scale=1.0, out=None, out_d
 
 def silu_mul(gu):
     if gu.is_cuda:
+        if gu.dtype == torch.bfloat16 and gu.is_contiguous():
+            return _sm().silu_and_mul(gu)
         return _seq().silu_mul(gu)
     return ref.silu_mul(gu)
 

@@ -80,6 +80,25 @@ def _declare(lib):
     sig("gllm_gemm_fp8_block", [P, P, P, P, P, L, I, I, I, P, P])
 
 
+_NEEDED = None     # csrc groups this process needs (None: all of them)
+
+
+def require(groups):
+    """Called before the first `load()` by an entry point that knows its model: a missing library is then built with
+    these kernel families only (csrc sub-directories). A library that holds fewer than needed is completed."""
+    global _NEEDED
+    _NEEDED = set(groups) if groups is not None else None
+
+
+def _lacking() -> bool:
+    from gllm_b200 import build as _build
+    held = _build.built_groups()
+    if held is None:
+        return False
+    need = _build.all_groups() if _NEEDED is None else (_NEEDED & _build.all_groups())
+    return not need <= held
+
+
 def load():
     global _LIB, _LIB_ERR
     if _LIB is not None:
@@ -87,12 +106,13 @@ def load():
     if _LIB_ERR is not None:
         raise _LIB_ERR
     try:
-        if not os.path.exists(LIB_PATH):
+        if not os.path.exists(LIB_PATH) or _lacking():
             # safety net: build in-tree on first use when a toolchain is present (takes about a minute); a box
             # without nvcc gets the loud error — there is no PyTorch fallback on the GPU path
             try:
                 from gllm_b200 import build as _build
-                _build.build()
+                held = _build.built_groups() if os.path.exists(LIB_PATH) else None
+                _build.build(groups=None if _NEEDED is None else (_NEEDED | (held or set())))
             except Exception as be:  # noqa: BLE001
                 raise FileNotFoundError(
                     f"{LIB_PATH} not found and the in-tree build failed ({be}) — run `python -m gllm_b200.build` "

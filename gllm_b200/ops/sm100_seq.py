@@ -36,7 +36,8 @@ def _L():
                                       I, P],
             "gllm_seq_gated_group_norm": [P, I, P, G, P, I, I, F, I, F, P, G, I, I, P],
             "gllm_seq_silu_mul": [P, G, I, I, P, I, P],
-            "gllm_seq_router_topk": [P, G, P, I, I, I, I, P, P, I, P],
+            "gllm_seq_router_select": [P, I, I, I, P, P, P],
+            "gllm_seq_gemm_simt_f32out": [P, G, P, G, P, G, I, I, I, I, P],
             "gllm_seq_routed_experts": [P, G, P, P, P, P, I, I, I, I, P, P, I, P],
             "gllm_seq_softcap": [P, G, I, I, F, I, P],
             "gllm_seq_conv_silu": [P, G, I, I, I, P, P, I, P, P, P, P, P, I, P],
@@ -45,6 +46,8 @@ def _L():
             "gllm_seq_gemm_simt": [P, G, P, G, P, G, I, I, I, I, P],
             "gllm_attn_decode_win": [P, G, P, P, P, G, P, P, I, I, I, I, I, I, I, F, I, P, P],
             "gllm_attn_prefill_win": [P, G, P, P, P, G, P, P, P, I, I, I, I, I, I, I, I, F, I, P, P],
+            "gllm_attn_decode_mask": [P, G, P, G, P, P, G, P, P, I, I, I, I, I, I, I, F, I, I, P, F, P],
+            "gllm_attn_prefill_mask": [P, G, P, G, P, P, G, P, P, P, I, I, I, I, I, I, I, I, F, I, I, P, F, P],
         }
         for name, args in sigs.items():
             fn = getattr(L, name)
@@ -124,8 +127,9 @@ def window_attention(q, k_cache, v_cache, block_table, seq_lens, query_start_loc
                      head_dim, window, sink, num_decode_seqs: int = 0, max_q_len: Optional[int] = None,
                      simt: bool = False, chunk: Optional[int] = None, v_dim: Optional[int] = None,
                      out_scale: float = 1.0, out: Optional[torch.Tensor] = None):
-    """Sliding-window (None / 0 = full causal) paged attention with an optional per-head softmax sink. bf16 with
-    head_dim 64 / 128 / 256 and pages of 8..64 tokens runs on the tensor-core paged-attention kernels
+    """Masked paged attention: sliding window (None / 0 = full causal) and / or chunk mask, optional per-head softmax
+    sink, values `v_dim` wide, result times `out_scale` into `out` (any row stride). bf16 with v_dim == head_dim
+    in 64 / 128 / 256 and pages of 8..64 tokens runs on the tensor-core paged-attention kernels
     (csrc/attn/paged_attention.cu: the first `num_decode_seqs` sequences, one token each, on the decode kernel, the
     rest on the prefill kernel); everything else (fp32, other head sizes or page sizes) on the plain kernel."""
     t = q.shape[0]
@@ -136,23 +140,24 @@ def window_attention(q, k_cache, v_cache, block_table, seq_lens, query_start_loc
     assert q.is_contiguous() and block_table.stride(1) == 1 and positions.dim() == 1
     assert out.stride(1) == 1 and out.dtype == q.dtype and v_cache.shape[3] == ps
     nseq = seq_lens.shape[0]
-    plain_only = bool(chunk) or v_dim != head_dim or out_scale != 1.0 or out.stride(0) != num_q_heads * v_dim
-    if not simt and not plain_only and q.dtype == torch.bfloat16 and head_dim in (64, 128, 256) and slab == 64 and ps >= 8 and \
+    # the tensor-core kernels store 8-byte vectors: rows and head offsets of `out` must keep that alignment
+    tc_ok = v_dim == head_dim and out.stride(0) % 4 == 0 and out.data_ptr() % 8 == 0
+    if not simt and tc_ok and q.dtype == torch.bfloat16 and head_dim in (64, 128, 256) and slab == 64 and ps >= 8 and \
             64 % ps == 0 and max_q_len is not None:
         L, st = _L(), stream_ptr()
         pages, hkv = k_cache.shape[0], k_cache.shape[1]
         if num_decode_seqs > 0:
-            check(L.gllm_attn_decode_win(_p(q), q.stride(0), _p(out), _p(k_cache), _p(v_cache), pages, _p(block_table),
-                                         _p(seq_lens), num_decode_seqs, 0, block_table.stride(0), num_q_heads, hkv,
-                                         head_dim, ps, float(scale), int(window or 0), _p(sink), st),
-                  "attn_decode_win")
+            check(L.gllm_attn_decode_mask(_p(q), q.stride(0), _p(out), out.stride(0), _p(k_cache), _p(v_cache), pages,
+                                          _p(block_table), _p(seq_lens), num_decode_seqs, 0, block_table.stride(0),
+                                          num_q_heads, hkv, head_dim, ps, float(scale), int(window or 0),
+                                          int(chunk or 0), _p(sink), float(out_scale), st), "attn_decode_mask")
             sm100._count()
         if nseq > num_decode_seqs:
-            check(L.gllm_attn_prefill_win(_p(q), q.stride(0), _p(out), _p(k_cache), _p(v_cache), pages,
-                                          _p(block_table), _p(seq_lens), _p(query_start_loc), nseq - num_decode_seqs,
-                                          num_decode_seqs, max_q_len, block_table.stride(0), num_q_heads, hkv,
-                                          head_dim, ps, float(scale), int(window or 0), _p(sink), st),
-                  "attn_prefill_win")
+            check(L.gllm_attn_prefill_mask(_p(q), q.stride(0), _p(out), out.stride(0), _p(k_cache), _p(v_cache), pages,
+                                           _p(block_table), _p(seq_lens), _p(query_start_loc), nseq - num_decode_seqs,
+                                           num_decode_seqs, max_q_len, block_table.stride(0), num_q_heads, hkv,
+                                           head_dim, ps, float(scale), int(window or 0), int(chunk or 0), _p(sink),
+                                           float(out_scale), st), "attn_prefill_mask")
             sm100._count()
         return out
     check(_L().gllm_seq_window_attention(_p(q), _p(k_cache), _p(v_cache), _p(block_table), block_table.stride(0),
@@ -266,13 +271,18 @@ def silu_mul(gu):
 
 
 def router_topk(h, w, top_k):
+    """fp32 logits h . w^T (plain GEMM with fp32 accumulation and fp32 result), then top-k + softmax over the chosen."""
     t, width = h.shape
-    assert h.stride(1) == 1 and w.is_contiguous() and h.dtype == w.dtype
+    e = w.shape[0]
+    assert h.stride(1) == 1 and w.is_contiguous() and h.dtype == w.dtype and e <= 1024
+    logits = torch.empty(t, e, dtype=torch.float32, device=h.device)
     wout = torch.empty(t, top_k, dtype=torch.float32, device=h.device)
     ids = torch.empty(t, top_k, dtype=torch.int32, device=h.device)
-    check(_L().gllm_seq_router_topk(_p(h), h.stride(0), _p(w), t, width, w.shape[0], top_k, _p(wout), _p(ids),
-                                    _f32(h), stream_ptr()), "seq_router_topk")
-    sm100._count()
+    L, st = _L(), stream_ptr()
+    check(L.gllm_seq_gemm_simt_f32out(_p(h), h.stride(0), _p(w), w.stride(0), _p(logits), e, t, e, width, _f32(h), st),
+          "seq_gemm_simt_f32out")
+    check(L.gllm_seq_router_select(_p(logits), t, e, top_k, _p(wout), _p(ids), st), "seq_router_select")
+    sm100._count(2)
     return wout, ids
 
 
