@@ -290,9 +290,8 @@ def _kernels_femolix(peaks):
     from gllm_b200.ops import sm100_moe
     row("router GEMM + topk_softmax (existing)",
         _time(lambda: sm100_moe.topk_softmax(sm100.linear(hh, wr), 2, True)), T2 * W * 2 + E * W * 2, like="router_topk")
-    gu = torch.randn(T2, 2 * 12288, device=dev).to(bf)
-    row("silu_mul 8192 x 12288", _time(lambda: S.silu_mul(gu)), T2 * 12288 * 6)
-    row("silu_and_mul (existing)", _time(lambda: sm100.silu_and_mul(gu)), T2 * 12288 * 6, like="silu_mul")
+    hd = hh[:64]
+    row("router_topk decode, 64 x 4096 x 64", _time(lambda: S.router_topk(hd, wr, 2)), E * W * 2)
     return out
 
 

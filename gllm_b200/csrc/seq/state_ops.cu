@@ -46,7 +46,7 @@ __global__ void __launch_bounds__(256) postnorm_kernel(float* __restrict__ x, co
 // pos * base^(-2i/rot). The token's cos / sin row is formed once per block, the angle in fp64 (no table, no maximum
 // position), the rotation itself in fp32.
 template <typename T>
-__global__ void __launch_bounds__(128) qk_norm_rope_kv_write_kernel(
+__global__ void __launch_bounds__(256) qk_norm_rope_kv_write_kernel(
     const T* __restrict__ qkv, long ld, int H, int G, int D, int Dv, const T* __restrict__ qn,
     const T* __restrict__ kn, float eps, const int* __restrict__ positions, int rot, double log2_base,
     T* __restrict__ q_out, T* __restrict__ kc, T* __restrict__ vc, const int* __restrict__ slots, int ps, int slab,
@@ -56,7 +56,7 @@ __global__ void __launch_bounds__(128) qk_norm_rope_kv_write_kernel(
   const int t = blockIdx.x;
   const int half = rot / 2;
   const double pos = (double)positions[t];
-  for (int i = threadIdx.x; i < half; i += 128) {
+  for (int i = threadIdx.x; i < half; i += 256) {
     double sn, cs;
     sincos(pos * exp2(-(2.0 * (double)i / (double)rot) * log2_base), &sn, &cs);
     cs_tab[i] = (float)cs;
@@ -64,7 +64,7 @@ __global__ void __launch_bounds__(128) qk_norm_rope_kv_write_kernel(
   }
   __syncthreads();
   const int slot = slots[t];
-  for (int head = warp; head < H + 2 * G; head += 4) {
+  for (int head = warp; head < H + 2 * G; head += 8) {
     if (head >= H + G) {
       if (slot < 0) continue;
       const int g = head - H - G;
@@ -105,7 +105,7 @@ __global__ void __launch_bounds__(128) linear_state_kernel(
     const float* __restrict__ dt_bias, const float* __restrict__ decay, float* __restrict__ state,
     const int* __restrict__ rec_slots, const int* __restrict__ seq_lens, const int* __restrict__ qsl, int H, int G,
     int D, int V, int silu_in, int unit_qk, float q_scale, int delta, float* __restrict__ out) {
-  constexpr int TCH = 8;
+  constexpr int TCH = 8;               // tokens staged per round (16 measured 2.4x slower: registers)
   extern __shared__ float sm[];
   float* sq = sm;                      // [TCH][2][D]: q row, k row
   float* sg = sm + TCH * 2 * D;        // [TCH][2]: g, beta
@@ -241,6 +241,72 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, long ld, int F, T* __r
   if (i >= total) return;
   const size_t t = i / F, f = i - t * F;
   out[i] = from_f<T>(silu_f(to_f(gu[t * ld + f])) * to_f(gu[t * ld + F + f]));
+}
+
+// Router logits for small batches: one warp per (token, expert), lanes over the width in a fixed order, fp32 result.
+template <typename T>
+__global__ void __launch_bounds__(128) router_logits_kernel(const T* __restrict__ h, long ldh, const T* __restrict__ w,
+                                                            int width, int E, float* __restrict__ logits) {
+  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int e = blockIdx.y * 4 + warp;
+  if (e >= E) return;
+  const T* hr = h + (size_t)t * ldh;
+  const T* wr = w + (size_t)e * width;
+  float acc = 0.f;
+  for (int i = lane; i < width; i += 32) acc = fmaf(to_f(hr[i]), to_f(wr[i]), acc);
+  acc = warp_sum(acc);
+  if (lane == 0) logits[(size_t)t * E + e] = acc;
+}
+
+// Router logits for large bf16 batches on the tensor cores, result kept in fp32: one warp computes 16 tokens x up to
+// NT * 8 experts with mma.sync m16n8k16 (bf16 products are exact in fp32, accumulation is fp32), operand fragments
+// read straight from global memory (the router weight stays in L1 / L2). width % 16 == 0, rows 4-byte aligned.
+template <int NT>
+__global__ void __launch_bounds__(128) router_logits_mma_kernel(const __nv_bfloat16* __restrict__ h, long ldh,
+                                                                const __nv_bfloat16* __restrict__ w, int ntok,
+                                                                int width, int E, float* __restrict__ logits) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t4 = lane & 3;
+  const int row0 = (blockIdx.x * 4 + warp) * 16;
+  const int e0 = blockIdx.y * NT * 8;
+  if (row0 >= ntok) return;
+  const int ra = min(row0 + g, ntok - 1), rb = min(row0 + g + 8, ntok - 1);   // clamped rows are never stored
+  const __nv_bfloat16* ha = h + (size_t)ra * ldh + 2 * t4;
+  const __nv_bfloat16* hb = h + (size_t)rb * ldh + 2 * t4;
+  float acc[NT][4];
+#pragma unroll
+  for (int n = 0; n < NT; ++n) { acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f; }
+  for (int k0 = 0; k0 < width; k0 += 16) {
+    uint32_t a[4];
+    a[0] = *reinterpret_cast<const uint32_t*>(ha + k0);
+    a[1] = *reinterpret_cast<const uint32_t*>(hb + k0);
+    a[2] = *reinterpret_cast<const uint32_t*>(ha + k0 + 8);
+    a[3] = *reinterpret_cast<const uint32_t*>(hb + k0 + 8);
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+      const int e = e0 + n * 8 + g;
+      uint32_t b0 = 0u, b1 = 0u;
+      if (e < E) {
+        const __nv_bfloat16* wr = w + (size_t)e * width + k0 + 2 * t4;
+        b0 = *reinterpret_cast<const uint32_t*>(wr);
+        b1 = *reinterpret_cast<const uint32_t*>(wr + 8);
+      }
+      asm volatile(
+          "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+          "{%0, %1, %2, %3};"
+          : "+f"(acc[n][0]), "+f"(acc[n][1]), "+f"(acc[n][2]), "+f"(acc[n][3])
+          : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+    }
+  }
+#pragma unroll
+  for (int n = 0; n < NT; ++n) {
+    const int e = e0 + n * 8 + 2 * t4;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const int r = row0 + g + (c >> 1) * 8, ee = e + (c & 1);
+      if (r < ntok && ee < E) logits[(size_t)r * E + ee] = acc[n][c];
+    }
+  }
 }
 
 // Router, second half: one warp per token over its fp32 logits [E] (the first half is the fp32-output GEMM): the
@@ -388,11 +454,11 @@ GLLM_EXPORT int gllm_seq_qk_norm_rope_kv_write(const void* qkv, long ld, int nto
   dim3 grid(ntok);
   const size_t smem = (size_t)(rot > 0 ? rot : 2) * sizeof(float);
   GLLM_BY_DTYPE(is_f32,
-                (qk_norm_rope_kv_write_kernel<bf16_t><<<grid, 128, smem, st>>>(
+                (qk_norm_rope_kv_write_kernel<bf16_t><<<grid, 256, smem, st>>>(
                     (const bf16_t*)qkv, ld, H, G, D, Dv, (const bf16_t*)qn, (const bf16_t*)kn, eps,
                     (const int*)positions, rot, log2_base, (bf16_t*)q_out, (bf16_t*)kc, (bf16_t*)vc,
                     (const int*)slots, ps, slab, slab_v)),
-                (qk_norm_rope_kv_write_kernel<float><<<grid, 128, smem, st>>>(
+                (qk_norm_rope_kv_write_kernel<float><<<grid, 256, smem, st>>>(
                     (const float*)qkv, ld, H, G, D, Dv, (const float*)qn, (const float*)kn, eps,
                     (const int*)positions, rot, log2_base, (float*)q_out, (float*)kc, (float*)vc, (const int*)slots,
                     ps, slab, slab_v)));
@@ -409,7 +475,7 @@ GLLM_EXPORT int gllm_seq_linear_state(const void* q, long ldq, const void* k, lo
   if (nseq <= 0) return 0;
   cudaStream_t st = (cudaStream_t)stream;
   dim3 grid(nseq, H, (V + 31) / 32);
-  const size_t smem = (size_t)(8 * 2 * D + 16) * sizeof(float);
+  const size_t smem = (size_t)(8 * 2 * D + 16) * sizeof(float);      // TCH rows of q and k + TCH (g, beta)
   int rc;
   if (is_f32)
     rc = state_dispatch<float>(grid, smem, st, q, ldq, k, ldk, v, ldv, beta, ldb, a, lda, (const float*)neg_a,
@@ -453,6 +519,32 @@ GLLM_EXPORT int gllm_seq_silu_mul(const void* gu, long ld, int ntok, int F, void
   GLLM_BY_DTYPE(is_f32,
                 (silu_mul_kernel<bf16_t><<<blocks, 256, 0, st>>>((const bf16_t*)gu, ld, F, (bf16_t*)out, total)),
                 (silu_mul_kernel<float><<<blocks, 256, 0, st>>>((const float*)gu, ld, F, (float*)out, total)));
+  CUDA_CHECK_RET(cudaGetLastError());
+  return 0;
+}
+
+GLLM_EXPORT int gllm_seq_router_logits(const void* h, long ldh, const void* w, int ntok, int width, int E,
+                                       void* logits, int is_f32, void* stream) {
+  if (ntok <= 0) return 0;
+  cudaStream_t st = (cudaStream_t)stream;
+  dim3 grid(ntok, (E + 3) / 4);
+  GLLM_BY_DTYPE(is_f32,
+                (router_logits_kernel<bf16_t><<<grid, 128, 0, st>>>((const bf16_t*)h, ldh, (const bf16_t*)w, width, E,
+                                                                    (float*)logits)),
+                (router_logits_kernel<float><<<grid, 128, 0, st>>>((const float*)h, ldh, (const float*)w, width, E,
+                                                                   (float*)logits)));
+  CUDA_CHECK_RET(cudaGetLastError());
+  return 0;
+}
+
+GLLM_EXPORT int gllm_seq_router_logits_mma(const void* h, long ldh, const void* w, int ntok, int width, int E,
+                                           void* logits, void* stream) {
+  if (ntok <= 0) return 0;
+  if (width % 16 != 0 || ldh % 2 != 0) return 2;
+  cudaStream_t st = (cudaStream_t)stream;
+  dim3 grid((ntok + 63) / 64, (E + 63) / 64);
+  router_logits_mma_kernel<8><<<grid, 128, 0, st>>>((const bf16_t*)h, ldh, (const bf16_t*)w, ntok, width, E,
+                                                    (float*)logits);
   CUDA_CHECK_RET(cudaGetLastError());
   return 0;
 }

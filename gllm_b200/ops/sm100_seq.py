@@ -37,6 +37,8 @@ def _L():
             "gllm_seq_gated_group_norm": [P, I, P, G, P, I, I, F, I, F, P, G, I, I, P],
             "gllm_seq_silu_mul": [P, G, I, I, P, I, P],
             "gllm_seq_router_select": [P, I, I, I, P, P, P],
+            "gllm_seq_router_logits": [P, G, P, I, I, I, P, I, P],
+            "gllm_seq_router_logits_mma": [P, G, P, I, I, I, P, P],
             "gllm_seq_gemm_simt_f32out": [P, G, P, G, P, G, I, I, I, I, P],
             "gllm_seq_routed_experts": [P, G, P, P, P, P, I, I, I, I, P, P, I, P],
             "gllm_seq_softcap": [P, G, I, I, F, I, P],
@@ -270,17 +272,31 @@ def silu_mul(gu):
     return out
 
 
-def router_topk(h, w, top_k):
-    """fp32 logits h . w^T (plain GEMM with fp32 accumulation and fp32 result), then top-k + softmax over the chosen."""
+_ROUTER_MMA_MIN_TOKENS = 256
+
+
+def router_topk(h, w, top_k, force: Optional[str] = None):
+    """fp32 router logits h . w^T, then the top_k largest per token and the softmax over the chosen (one warp per
+    token). Logits: small batches, one warp per (token, expert); large bf16 batches on the tensor cores (mma.sync,
+    fp32 accumulation and fp32 result); large fp32 batches, the plain GEMM with fp32 result."""
     t, width = h.shape
     e = w.shape[0]
     assert h.stride(1) == 1 and w.is_contiguous() and h.dtype == w.dtype and e <= 1024
-    logits = torch.empty(t, e, dtype=torch.float32, device=h.device)
     wout = torch.empty(t, top_k, dtype=torch.float32, device=h.device)
     ids = torch.empty(t, top_k, dtype=torch.int32, device=h.device)
+    logits = torch.empty(t, e, dtype=torch.float32, device=h.device)
     L, st = _L(), stream_ptr()
-    check(L.gllm_seq_gemm_simt_f32out(_p(h), h.stride(0), _p(w), w.stride(0), _p(logits), e, t, e, width, _f32(h), st),
-          "seq_gemm_simt_f32out")
+    mma_ok = h.dtype == torch.bfloat16 and width % 16 == 0 and h.stride(0) % 2 == 0 and h.data_ptr() % 4 == 0
+    path = force or ("token" if t < _ROUTER_MMA_MIN_TOKENS else ("mma" if mma_ok else "gemm"))
+    if path == "token":
+        check(L.gllm_seq_router_logits(_p(h), h.stride(0), _p(w), t, width, e, _p(logits), _f32(h), st),
+              "seq_router_logits")
+    elif path == "mma":
+        check(L.gllm_seq_router_logits_mma(_p(h), h.stride(0), _p(w), t, width, e, _p(logits), st),
+              "seq_router_logits_mma")
+    else:
+        check(L.gllm_seq_gemm_simt_f32out(_p(h), h.stride(0), _p(w), w.stride(0), _p(logits), e, t, e, width, _f32(h),
+                                          st), "seq_gemm_simt_f32out")
     check(L.gllm_seq_router_select(_p(logits), t, e, top_k, _p(wout), _p(ids), st), "seq_router_select")
     sm100._count(2)
     return wout, ids

@@ -82,9 +82,17 @@ def test_kernels_against_unfused_ops(dt, tol):
     # router: ids exact (random logits have no near ties), weights close
     hh, wr = torch.randn(T, W, device=DEV).to(dt), torch.randn(11, W, device=DEV).to(dt)
     for k in (1, 2, 11):
-        w1, i1 = S.router_topk(hh, wr, k)
         w2, i2 = ref.router_topk(hh, wr, k)
-        assert torch.equal(i1, i2) and close(w1, w2, 1e-4)
+        for path in ("token", "gemm"):
+            w1, i1 = S.router_topk(hh, wr, k, force=path)
+            assert torch.equal(i1, i2) and close(w1, w2, 1e-4), (k, path)
+    if dt == torch.bfloat16:          # tensor-core logits: ragged token and expert counts, two expert tiles
+        for tt, ee, ww in ((37, 11, 208), (300, 70, 64), (64, 8, 16), (1000, 64, 512)):
+            hb = torch.randn(tt, ww + 16, device=DEV).to(dt)[:, :ww]
+            wb = torch.randn(ee, ww, device=DEV).to(dt)
+            w2, i2 = ref.router_topk(hb, wb, 2)
+            w1, i1 = S.router_topk(hb, wb, 2, force="mma")
+            assert torch.equal(i1, i2) and close(w1, w2, 1e-4), (tt, ee, ww)
     # plain experts
     E, F = 5, 24
     w13, w2_ = (torch.randn(E, 2 * F, W, device=DEV) * W ** -0.5).to(dt), (torch.randn(E, W, F, device=DEV) * F ** -0.5).to(dt)
