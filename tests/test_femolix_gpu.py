@@ -73,12 +73,12 @@ def test_kernels_against_unfused_ops(dt, tol):
     x = torch.randn(T, W, device=DEV)
     y, w = torch.randn(T, W, device=DEV).to(dt), (torch.rand(W, device=DEV) + 0.5).to(dt)
     x1, x2 = x.clone(), x.clone()
-    h1, h2 = S.postnorm(x1, y, 2.5, w, 1e-5, dt), ref.postnorm(x2, y, 2.5, w, 1e-5, dt)
+    h1, h2 = S.postnorm(x1, y, 1.75, w, 1e-5, dt), ref.postnorm(x2, y, 1.75, w, 1e-5, dt)
     assert close(h1, h2, tol) and close(x1, x2, 1e-5)
     gu = torch.randn(T, 2 * 50, device=DEV).to(dt)
     assert close(S.silu_mul(gu), ref.silu_mul(gu), tol)
     z = (torch.randn(T, 77, device=DEV) * 20).to(dt)
-    assert close(S.softcap(z.clone(), 15.0), ref.softcap(z, 15.0), tol)
+    assert close(S.softcap(z.clone(), 12.0), ref.softcap(z, 12.0), tol)
     # router: ids exact (random logits have no near ties), weights close
     hh, wr = torch.randn(T, W, device=DEV).to(dt), torch.randn(11, W, device=DEV).to(dt)
     for k in (1, 2, 11):
@@ -99,7 +99,7 @@ def test_kernels_against_unfused_ops(dt, tol):
     wt, ids = ref.router_topk(hh, wr[:E], 2)
     assert close(S.routed_experts(hh, w13, w2_, wt, ids), ref.fused_experts(hh, w13, w2_, wt, ids, None), tol)
     # q/k norm + rotation + cache write, then chunk / window attention on the plain kernel, odd head sizes
-    for D, Dv, rot in ((48, 96, 48), (8, 4, 6), (64, 64, 32), (20, 36, 0)):
+    for D, Dv, rot in ((40, 72, 24), (8, 4, 6), (64, 64, 32), (20, 36, 0)):
         H, G, ps = 6, 2, 16
         qlens, ctx = [5, 1, 30], [17, 40, 0]
         qsl, sl, bt, pos, slots = _batch(qlens, ctx, ps, 32)
@@ -110,8 +110,8 @@ def test_kernels_against_unfused_ops(dt, tol):
         qn, kn = torch.randn(D, device=DEV).to(dt), torch.randn(D, device=DEV).to(dt)
         kc2, vc2 = kc.clone(), vc.clone()
         big = pos + 5000                                   # far positions: angles need more than fp32 products
-        q1 = S.qk_norm_rope_kv_write(qkv, H, G, D, Dv, qn, kn, 1e-5, big, rot, 20000.0, kc, vc, slots)
-        q2 = ref.qk_norm_rope_kv_write(qkv, H, G, D, Dv, qn, kn, 1e-5, big, rot, 20000.0, kc2, vc2, slots)
+        q1 = S.qk_norm_rope_kv_write(qkv, H, G, D, Dv, qn, kn, 1e-5, big, rot, 5000.0, kc, vc, slots)
+        q2 = ref.qk_norm_rope_kv_write(qkv, H, G, D, Dv, qn, kn, 1e-5, big, rot, 5000.0, kc2, vc2, slots)
         assert close(q1, q2, tol) and close(kc, kc2, tol) and torch.equal(vc, vc2)
         sink = torch.randn(H, device=DEV)
         for wn, ch, sk in ((None, 7, None), (None, 16, None), (5, 12, sink), (None, 1, None), (None, None, None)):
@@ -122,7 +122,7 @@ def test_kernels_against_unfused_ops(dt, tol):
             assert close(a1, a2, tol), (D, wn, ch)
             assert joint[:, :8].abs().max().item() == 0
     # matrix-state recurrences with carried state, grouped heads, padded value columns
-    for Hh, Gq, D, V, delta in ((4, 2, 64, 32, True), (2, 2, 64, 32, False), (3, 1, 5, 3, True), (2, 2, 48, 40, False),
+    for Hh, Gq, D, V, delta in ((4, 2, 32, 24, True), (2, 2, 64, 48, False), (3, 1, 5, 3, True), (2, 2, 48, 40, False),
                                 (1, 1, 128, 16, True)):
         qlens, ctx = [5, 1, 30], [17, 40, 0]
         qsl, sl, _, _, _ = _batch(qlens, ctx, 16, 32)
@@ -181,7 +181,7 @@ def test_tensor_core_attention_with_chunk_mask_and_strided_output():
 def test_grouped_gemm_experts_match_plain_experts():
     from gllm_b200.layers.moe import SelectedSoftmaxMoE
     torch.manual_seed(2)
-    W, F, E = 256, 64, 8
+    W, F, E = 384, 128, 8
     m = SelectedSoftmaxMoE(E, 2, W, F, torch.bfloat16, DEV)
     assert m.interleaved
     m.router_w.data.copy_(torch.randn(E, W) * 0.3)
