@@ -94,12 +94,13 @@ __global__ void __launch_bounds__(256) qk_norm_rope_kv_write_kernel(
 }
 
 // Matrix-state recurrence, one block per (sequence, head, 32 value columns). A value column's D state entries are
-// split over 4 adjacent lanes (entry d = part + 4 j), NS per lane in registers; per token
+// split over PARTS adjacent lanes (entry d = part + PARTS j), NS per lane in registers; per token
 //     S <- g S;  u = delta ? beta (v - S^T k) : v;  S <- S + k u^T;  o = S^T q
-// costs two register passes and two 4-lane shuffles. q / k rows and the per-token g, beta of TCH tokens are staged
+// costs two register passes and two PARTS-lane shuffle reductions (PARTS = 8 for head sizes >= 128: half the
+// registers per thread, twice the warps in flight). q / k rows and the per-token g, beta of TCH tokens are staged
 // in shared memory by the whole block (SiLU, unit length and the q scale applied there).
-template <typename T, int NS>
-__global__ void __launch_bounds__(128) linear_state_kernel(
+template <typename T, int NS, int PARTS>
+__global__ void __launch_bounds__(32 * PARTS) linear_state_kernel(
     const T* __restrict__ q, long ldq, const T* __restrict__ k, long ldk, const T* __restrict__ v, long ldv,
     const T* __restrict__ beta, long ldb, const T* __restrict__ a, long lda, const float* __restrict__ neg_a,
     const float* __restrict__ dt_bias, const float* __restrict__ decay, float* __restrict__ state,
@@ -111,7 +112,8 @@ __global__ void __launch_bounds__(128) linear_state_kernel(
   float* sg = sm + TCH * 2 * D;        // [TCH][2]: g, beta
   const int s = blockIdx.x, h = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int vl = threadIdx.x >> 2, part = threadIdx.x & 3;
+  constexpr int NT = 32 * PARTS, NW = PARTS;       // threads and warps per block
+  const int vl = threadIdx.x / PARTS, part = threadIdx.x % PARTS;
   const int vcol = blockIdx.z * 32 + vl;
   const bool active = vcol < V;
   const int vc = active ? vcol : V - 1;          // idle lanes mirror the last column (loads only)
@@ -122,14 +124,14 @@ __global__ void __launch_bounds__(128) linear_state_kernel(
   float S[NS];
 #pragma unroll
   for (int j = 0; j < NS; ++j) {
-    const int d = part + 4 * j;
+    const int d = part + PARTS * j;
     S[j] = (carried && d < D) ? st[(size_t)d * V + vc] : 0.f;
   }
   const int kvh = h / (H / G);
   for (int t0 = q0; t0 < q1; t0 += TCH) {
     const int nt = min(TCH, q1 - t0);
     __syncthreads();                             // the previous chunk's rows are consumed
-    for (int idx = threadIdx.x; idx < nt * 2 * D; idx += 128) {
+    for (int idx = threadIdx.x; idx < nt * 2 * D; idx += NT) {
       const int kk = idx / (2 * D), r = idx - kk * 2 * D;
       float f = r < D ? to_f(q[(size_t)(t0 + kk) * ldq + (size_t)kvh * D + r])
                       : to_f(k[(size_t)(t0 + kk) * ldk + (size_t)kvh * D + r - D]);
@@ -150,7 +152,7 @@ __global__ void __launch_bounds__(128) linear_state_kernel(
     }
     __syncthreads();
     if (unit_qk || q_scale != 1.0f) {
-      for (int row = warp; row < 2 * nt; row += 4) {      // row = token * 2 + (0: q, 1: k)
+      for (int row = warp; row < 2 * nt; row += NW) {      // row = token * 2 + (0: q, 1: k)
         float* ptr = sq + (size_t)row * D;
         float sc = (row & 1) ? 1.0f : q_scale;
         if (unit_qk) {
@@ -181,24 +183,24 @@ __global__ void __launch_bounds__(128) linear_state_kernel(
           float dot = 0.f;
 #pragma unroll
           for (int j = 0; j < NS; ++j) {
-            const int d = part + 4 * j;
+            const int d = part + PARTS * j;
             if (d < D) dot = fmaf(S[j], kr[d], dot);
           }
-          dot += __shfl_xor_sync(0xffffffffu, dot, 1);
-          dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+#pragma unroll
+          for (int o = 1; o < PARTS; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
           u = b * (u - g * dot);
         }
         float o = 0.f;
 #pragma unroll
         for (int j = 0; j < NS; ++j) {
-          const int d = part + 4 * j;
+          const int d = part + PARTS * j;
           if (d < D) {
             S[j] = fmaf(kr[d], u, g * S[j]);
             o = fmaf(S[j], qq[d], o);
           }
         }
-        o += __shfl_xor_sync(0xffffffffu, o, 1);
-        o += __shfl_xor_sync(0xffffffffu, o, 2);
+#pragma unroll
+        for (int sh = 1; sh < PARTS; sh <<= 1) o += __shfl_xor_sync(0xffffffffu, o, sh);
         if (active && part == 0) out[(size_t)(t0 + kk) * H * V + (size_t)h * V + vcol] = o;
       }
     }
@@ -206,7 +208,7 @@ __global__ void __launch_bounds__(128) linear_state_kernel(
   if (st != nullptr && active) {
 #pragma unroll
     for (int j = 0; j < NS; ++j) {
-      const int d = part + 4 * j;
+      const int d = part + PARTS * j;
       if (d < D) st[(size_t)d * V + vcol] = S[j];
     }
   }
@@ -409,17 +411,17 @@ int state_dispatch(dim3 grid, size_t smem, cudaStream_t st, const void* q, long 
                    const void* v, long ldv, const void* beta, long ldb, const void* a, long lda, const float* neg_a,
                    const float* dt_bias, const float* decay, float* state, const int* rec_slots, const int* seq_lens,
                    const int* qsl, int H, int G, int D, int V, int silu_in, int unit_qk, float q_scale, int delta,
-                   float* out) {
-#define GLLM_STATE(NS)                                                                                              \
-  linear_state_kernel<T, NS><<<grid, 128, smem, st>>>((const T*)q, ldq, (const T*)k, ldk, (const T*)v, ldv,         \
+                   float* out, int parts) {
+#define GLLM_STATE(NS, PARTS)                                                                                       \
+  linear_state_kernel<T, NS, PARTS><<<grid, 32 * PARTS, smem, st>>>((const T*)q, ldq, (const T*)k, ldk, (const T*)v, ldv, \
                                                       (const T*)beta, ldb, (const T*)a, lda, neg_a, dt_bias, decay, \
                                                       state, rec_slots, seq_lens, qsl, H, G, D, V, silu_in, unit_qk, \
                                                       q_scale, delta, out)
-  if (D <= 16) GLLM_STATE(4);
-  else if (D <= 32) GLLM_STATE(8);
-  else if (D <= 64) GLLM_STATE(16);
-  else if (D <= 128) GLLM_STATE(32);
-  else if (D <= 256) GLLM_STATE(64);
+  if (D <= 16) GLLM_STATE(4, 4);
+  else if (D <= 32) GLLM_STATE(8, 4);
+  else if (D <= 64) GLLM_STATE(16, 4);
+  else if (D <= 128) { if (parts == 8) GLLM_STATE(16, 8); else GLLM_STATE(32, 4); }
+  else if (D <= 256) { if (parts == 8) GLLM_STATE(32, 8); else GLLM_STATE(64, 4); }
   else return 2;
 #undef GLLM_STATE
   return 0;
@@ -471,7 +473,7 @@ GLLM_EXPORT int gllm_seq_linear_state(const void* q, long ldq, const void* k, lo
                                       const void* dt_bias, const void* decay, void* state, const void* rec_slots,
                                       const void* seq_lens, const void* qsl, int nseq, int H, int G, int D, int V,
                                       int silu_in, int unit_qk, float q_scale, int delta, void* out, int is_f32,
-                                      void* stream) {
+                                      int parts, void* stream) {
   if (nseq <= 0) return 0;
   cudaStream_t st = (cudaStream_t)stream;
   dim3 grid(nseq, H, (V + 31) / 32);
@@ -481,12 +483,12 @@ GLLM_EXPORT int gllm_seq_linear_state(const void* q, long ldq, const void* k, lo
     rc = state_dispatch<float>(grid, smem, st, q, ldq, k, ldk, v, ldv, beta, ldb, a, lda, (const float*)neg_a,
                                (const float*)dt_bias, (const float*)decay, (float*)state, (const int*)rec_slots,
                                (const int*)seq_lens, (const int*)qsl, H, G, D, V, silu_in, unit_qk, q_scale, delta,
-                               (float*)out);
+                               (float*)out, parts);
   else
     rc = state_dispatch<bf16_t>(grid, smem, st, q, ldq, k, ldk, v, ldv, beta, ldb, a, lda, (const float*)neg_a,
                                 (const float*)dt_bias, (const float*)decay, (float*)state, (const int*)rec_slots,
                                 (const int*)seq_lens, (const int*)qsl, H, G, D, V, silu_in, unit_qk, q_scale, delta,
-                                (float*)out);
+                                (float*)out, parts);
   if (rc) return rc;
   CUDA_CHECK_RET(cudaGetLastError());
   return 0;

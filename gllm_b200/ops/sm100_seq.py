@@ -33,7 +33,7 @@ def _L():
             "gllm_seq_qk_norm_rope_kv_write": [P, G, I, I, I, I, I, P, P, F, P, I, ctypes.c_double, P, P, P, P, I, I, I,
                                                I, P],
             "gllm_seq_linear_state": [P, G, P, G, P, G, P, G, P, G, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, P,
-                                      I, P],
+                                      I, I, P],
             "gllm_seq_gated_group_norm": [P, I, P, G, P, I, I, F, I, F, P, G, I, I, P],
             "gllm_seq_silu_mul": [P, G, I, I, P, I, P],
             "gllm_seq_router_select": [P, I, I, I, P, P, P],
@@ -241,11 +241,17 @@ def linear_state_scan(q, k, v, beta, a, neg_a, dt_bias, decay, state, rec_slots,
     assert (decay is None) != (a is None) and (not delta or beta is not None)
     out = torch.empty(t, heads * v_dim, dtype=torch.float32, device=q.device)
     ld = lambda x: x.stride(0) if x is not None else 0   # noqa: E731
+    # long chunks on a grid that leaves SMs idle: 8 lanes per state column (twice the warps on the serial chain;
+    # 4 x 2048 tokens, head size 128: 8 heads 1.9x faster, 32 heads 1.4x slower than 4 lanes). Otherwise 4: decode-like
+    # batches want the wider contiguous runs of the state rows, whose read + write is all that a single token costs
+    nseq = seq_lens.shape[0]
+    blocks = nseq * heads * ((v_dim + 31) // 32)
+    parts = 8 if (dim > 64 and t >= 16 * nseq and blocks <= 2 * _NUM_SMS) else 4
     check(_L().gllm_seq_linear_state(_p(q), q.stride(0), _p(k), k.stride(0), _p(v), v.stride(0), _p(beta), ld(beta),
                                      _p(a), ld(a), _p(neg_a), _p(dt_bias), _p(decay), _p(state), _p(rec_slots),
                                      _p(seq_lens), _p(query_start_loc), seq_lens.shape[0], heads, qk_heads, dim, v_dim,
                                      int(silu_in), int(unit_qk), float(q_scale), int(delta), _p(out), _f32(q),
-                                     stream_ptr()), "seq_linear_state")
+                                     parts, stream_ptr()), "seq_linear_state")
     sm100._count()
     return out
 
@@ -273,6 +279,7 @@ def silu_mul(gu):
 
 
 _ROUTER_MMA_MIN_TOKENS = 256
+_NUM_SMS = 148
 
 
 def router_topk(h, w, top_k, force: Optional[str] = None):

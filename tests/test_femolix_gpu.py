@@ -123,8 +123,9 @@ def test_kernels_against_unfused_ops(dt, tol):
             assert joint[:, :8].abs().max().item() == 0
     # matrix-state recurrences with carried state, grouped heads, padded value columns
     for Hh, Gq, D, V, delta in ((4, 2, 32, 24, True), (2, 2, 64, 48, False), (3, 1, 5, 3, True), (2, 2, 48, 40, False),
-                                (1, 1, 128, 16, True)):
-        qlens, ctx = [5, 1, 30], [17, 40, 0]
+                                (1, 1, 128, 16, True), (2, 1, 128, 40, True), (2, 2, 192, 8, False)):
+        # head sizes above 64 take the 8-lanes-per-column form when the chunks are long
+        qlens, ctx = ([40, 1, 70], [17, 40, 0]) if (D > 64 and V != 16) else ([5, 1, 30], [17, 40, 0])
         qsl, sl, _, _, _ = _batch(qlens, ctx, 16, 32)
         Tt = sum(qlens)
         rs = torch.tensor([2, 0, 3], dtype=torch.int32, device=DEV)
