@@ -1,5 +1,5 @@
 // Helpers shared by the kernels of the layer-list decoders (csrc/seq): dtype conversion, warp / block reductions,
-// row -> sequence lookup, paged-cache indexing. Included inside each file's anonymous namespace users.
+// row -> sequence lookup, paged-cache indexing. Each .cu file pulls them in with `using namespace seqk`.
 #pragma once
 #include <cuda_bf16.h>
 

@@ -1,7 +1,8 @@
 // Kernels of the norm-after-sum layer-list decoders (models/hybrid.py, block "postnorm"): the fused residual update
 // x <- rms(alpha x + y) w, per-head q/k RMS norm + rotate-half rotary + paged K / V cache write, the matrix-state
 // linear recurrences (gated delta rule, constant-decay linear attention) with slot-indexed fp32 state, the grouped
-// RMS norm with a gate, SiLU-gated product, the fp32 top-k router with softmax over the chosen logits, plain
+// RMS norm with a gate, SiLU-gated product, fp32 router logits (per-warp dots or mma.sync tiles) and the top-k
+// selection with softmax over the chosen logits, plain
 // per-slot expert kernels for shapes / dtypes the grouped tcgen05 GEMM does not take, and the logit cap.
 //
 // Templated on the compute dtype T (bf16 or float); norms, gates, decays, softplus, the router, the recurrences and
